@@ -1,0 +1,150 @@
+/*
+ * q40b200 — C ABI of the B200 (sm_100a) kernels for the Q4_0 decode hot path.
+ *
+ * Conventions for every entry point
+ *   - all data pointers are DEVICE pointers owned by the caller; nothing is allocated,
+ *     freed or retained across the boundary;
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = legacy default
+ *     stream) and the call returns without synchronising the host;
+ *   - return value: 0 = enqueued, negative = argument error (Q40_E_*), positive = the
+ *     cudaError_t of a failed launch;  q40_strerror() turns either into text;
+ *   - "half" means IEEE binary16 stored as 2 bytes; Q4_0 here is the reference's format:
+ *     signed 4-bit codes in [-8,7], one fp16 scale per `group` consecutive elements
+ *     (group = 64 is the reference's fixed choice, 32 is also accepted), two groups
+ *     (2j, 2j+1) packed into one row of `group` bytes: byte i = code[2j][i] << 4 |
+ *     code[2j+1][i] & 0xF.
+ *
+ * Each declaration cites the reference interface it stands in for, as file:line of the
+ * reference project (hongyihuang/spec-mcts).
+ */
+#ifndef Q40B200_H
+#define Q40B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define Q40_OK 0
+#define Q40_E_NULL (-1)      /* a required pointer is NULL                         */
+#define Q40_E_SHAPE (-2)     /* a size violates a divisibility or range rule       */
+#define Q40_E_ALIGN (-3)     /* a pointer or stride is not aligned as documented   */
+#define Q40_E_WORKSPACE (-4) /* workspace missing or smaller than *_workspace_bytes */
+#define Q40_E_UNSUPPORTED (-5)
+
+const char* q40_strerror(int status);
+/* Library/ABI version, bumped when a signature changes. */
+int q40_abi_version(void);
+
+/* ---- Q4_0 pack / unpack ------------------------------------------------------------ */
+
+/* w[n] fp16 (row-major, any logical shape) -> q[n/2] bytes viewed as [n/(2*group), group],
+ * s[n/group] fp16.  Bit-exact with quantize_q40 for fp16 input: scale = fp16(absmax/7),
+ * code = int8(rint(fp16(w/scale))), non-finite quotient -> 0.
+ * n % (2*group) == 0; w, q 16-byte aligned.
+ * Replaces: quantize_q40 (triton_kernels.py:12-41) and, with correct rounding,
+ * triton_q_int40 (triton_kernels.py:109-152). */
+int q40_quantize(const void* w, void* q, void* s, int64_t n, int group, void* stream);
+
+/* Same packer applied to n_rows separate rows of row_len fp16 elements each; row r is
+ * read at w + r*w_row_stride (elements) and written at q + r*q_row_stride (bytes) and
+ * s + r*s_row_stride (elements), so the new token rows of a strided KV cache can be
+ * quantised in place.  row_len % (2*group) == 0, strides keep 16-byte alignment.
+ * Replaces the intent of triton_q_int40_sliced (triton_kernels.py:154-200) and the
+ * per-step re-quantisation in Attention.forward (hf_model_q40_kv_shared.py:365-371). */
+int q40_quantize_rows(const void* w, int64_t w_row_stride, void* q, int64_t q_row_stride,
+                      void* s, int64_t s_row_stride, int64_t n_rows, int row_len, int group,
+                      void* stream);
+
+/* q, s -> out[n] fp16, out = fp16(code * scale).  Bit-exact with dequantize_q40.
+ * Replaces: dequantize_q40 (triton_kernels.py:43-56), triton_deq_int40 (:58-107). */
+int q40_dequantize(const void* q, const void* s, void* out, int64_t n, int group, void* stream);
+
+/* ---- fused dequant-matmul ------------------------------------------------------------ */
+
+/* Workspace (bytes) that q40_gemm_kn / q40_gemm_nk need for this problem; the buffer
+ * must be zero-filled once when it is created (the kernels leave it zeroed) and must not
+ * be shared by calls that can overlap on the GPU. */
+size_t q40_gemm_workspace_bytes(int M, int N, int K);
+
+/* C[M,N] = A[M,K] @ deq(B)[K,N], B quantised from a row-major [K,N] matrix (groups along
+ * N; the on-disk orientation): bw viewed as [K, N/2] bytes, bs as [K, N/group] fp16.
+ * fp16 in, fp32 accumulate, fp16 out.  lda/ldc in elements.  N % (2*group) == 0.
+ * Replaces: matmul_q40 (triton_kernels.py:357-500), called by LinearQ4_0.forward
+ * (hf_model_q40_kv_shared.py:228-236). */
+int q40_gemm_kn(const void* a, int64_t lda, const void* bw, const void* bs, void* c,
+                int64_t ldc, int M, int N, int K, int group, void* workspace,
+                size_t workspace_bytes, void* stream);
+
+/* Y[M,N] = X[M,K] @ deq(W)[N,K]^T, W quantised from a row-major [N,K] matrix (groups
+ * along K): wq viewed as [N*K/(2*group), group], ws as [N*K/group].  K % (2*group) == 0.
+ * Replaces: dequantize_q40 + F.linear in LinearQ4_0.forward (quantize.py:235-246,
+ * hf_model_q40.py:222-233). */
+int q40_gemm_nk(const void* x, int64_t ldx, const void* wq, const void* ws, void* y,
+                int64_t ldy, int M, int N, int K, int group, void* workspace,
+                size_t workspace_bytes, void* stream);
+
+/* ---- decode attention (one query token per branch) ---------------------------------- */
+
+/* q[B,H,D], k/v[B,Hkv,L,D] contiguous fp16 -> o[B,H,D]; scale 1/sqrt(D); D == 128;
+ * H % Hkv == 0.  fp32 online softmax.
+ * Replaces: flash_attn (triton_kernels.py:559-647). */
+int q40_attn_decode(const void* q, const void* k, const void* v, void* o, int B, int L, int H,
+                    int Hkv, int D, void* stream);
+
+/* Paged decode attention.  kpool/vpool [Hkv, P, D] fp16 hold P token slots per kv head.
+ * page_tbl[B, tbl_stride] (idx_bytes = 2: int16, 4: int32) lists page ids; token t of
+ * branch b is slot page_tbl[b][t / page_size] * page_size + t % page_size.  seq_lens[B]
+ * int32 gives each branch's length, or NULL = every branch has length Lmax.
+ * page_size = 1 with an int16 table is the reference's layout.
+ * Replaces: page_flash_attn (triton_kernels.py:700-789). */
+int q40_attn_paged(const void* page_tbl, int idx_bytes, int64_t tbl_stride, const int32_t* seq_lens,
+                   const void* q, const void* kpool, const void* vpool, void* o, int P, int B,
+                   int Lmax, int H, int Hkv, int D, int page_size, void* stream);
+
+/* Bytes of fp32 scratch q40_attn_shared_prefix needs (partial max / sum / output of each
+ * prefix split).  No initialisation required. */
+size_t q40_attn_shared_prefix_workspace_bytes(int B, int H, int D, int prefix_len);
+
+/* Shared-prefix decode attention: all B branches attend to the same prefix (key t of kv
+ * head h at prefix_k + t*prefix_key_stride + h*prefix_head_stride, in elements; strides are
+ * multiples of 8; the prefix is read once per CTA and applied to every branch)
+ * and then to their private paged suffix (arguments as q40_attn_paged, lengths = suffix
+ * lengths, may be 0).  Result is attention over cat(prefix, suffix_b).
+ * Replaces: chunk_attn (triton_kernels.py:1150-1231) and the materialised
+ * cat(prompt.expand(B), suffix) + SDPA in Attention.forward
+ * (hf_model_q40_kv_shared.py:375-376, 405). */
+int q40_attn_shared_prefix(const void* q, const void* prefix_k, const void* prefix_v,
+                           int prefix_len, int64_t prefix_key_stride, int64_t prefix_head_stride,
+                           const void* page_tbl, int idx_bytes,
+                           int64_t tbl_stride, const int32_t* seq_lens, const void* kpool,
+                           const void* vpool, void* o, int P, int B, int Lmax, int H, int Hkv,
+                           int D, int page_size, void* workspace, size_t workspace_bytes,
+                           void* stream);
+
+/* ---- epilogue math with the reference's rounding points ------------------------------ */
+
+/* y[r,:] = fp16(fp16(x32 * rsqrt(mean(x32^2) + eps)) * w); if `residual` is non-NULL the
+ * row is first replaced by h = fp16(x + residual), which is also written to h_out.
+ * Replaces: RMSNorm.forward (hf_model_q40_kv_shared.py:123-134) and the residual adds of
+ * TransformerBlock.forward (:463-466). */
+int q40_rmsnorm(const void* x, const void* residual, const void* w, void* y, void* h_out,
+                int rows, int dim, float eps, void* stream);
+
+/* In-place rotary embedding of x[rows, n_heads, D] with per-row positions pos[rows] (int32)
+ * and fp16 tables cos/sin [n_pos, D/2]: out = fp16(fp16(x*cos) + fp16(rot(x)*sin)),
+ * rot(x) = cat(-x[D/2:], x[:D/2]).
+ * Replaces: apply_rotary_emb / rotate_half (hf_model_q40_kv_shared.py:166-203). */
+int q40_rope(void* x, const int32_t* pos, const void* cos_tbl, const void* sin_tbl, int rows,
+             int n_heads, int D, int64_t row_stride, void* stream);
+
+/* y = fp16(fp16(silu(a)) * b), n elements.
+ * Replaces: F.silu(w1(x)) * w3(x) in FeedForward.forward (hf_model_q40_kv_shared.py:434). */
+int q40_silu_mul(const void* a, const void* b, void* y, int64_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q40B200_H */

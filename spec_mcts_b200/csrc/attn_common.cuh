@@ -1,0 +1,31 @@
+// Declarations shared by the attention kernels.
+#pragma once
+#include "q40_common.cuh"
+
+namespace q40 {
+
+constexpr int ATTN_D = 128;  // head dim of every supported model (CodeLlama 7B/70B)
+
+inline float attn_scale_log2(int D) { return (1.0f / sqrtf((float)D)) * 1.4426950408889634f; }
+
+struct BranchArgs {
+  const __half* q;        // [B, H, D]
+  const __half* k;        // contiguous: [B,Hkv,L,D]; paged: pool [Hkv,P,D]
+  const __half* v;
+  __half* o;              // [B, H, D]
+  const void* tbl;        // page table or nullptr
+  int64_t tbl_stride;
+  const int32_t* seq_lens;  // per-branch length or nullptr (= L)
+  int L, H, Hkv, P, page_size;
+  // optional partial results of a prefix pass over rows (b, h), log2 domain, un-normalised
+  const float* pm;        // [nsp][B*H]
+  const float* pl;        // [nsp][B*H]
+  const float* po;        // [nsp][B*H][128]
+  int nsp;
+  float scale_log2;       // 1/sqrt(D) * log2(e)
+};
+
+// defined in attn_branch.cu; mode 0 contiguous, 1 paged/int16 ids, 2 paged/int32 ids
+int launch_branch(const BranchArgs& a, int mode, int B, cudaStream_t st);
+
+}  // namespace q40

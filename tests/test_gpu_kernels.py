@@ -1,0 +1,345 @@
+"""GPU parity tests: the CUDA kernels (called through the C ABI via the Python surface that
+mirrors the reference's triton_kernels module) against the CPU oracle and the golden
+vectors generated from the reference.  Pack/unpack must be bit-exact; matmul and attention
+must agree within rel 2e-2 / abs 1e-2 in fp16 (the tolerance of the specification)."""
+import hashlib
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import q40_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 2e-2, 1e-2
+
+
+@pytest.fixture(scope="module")
+def K():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from spec_mcts_b200 import kernels
+    return kernels
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+def assert_bits_equal(a, b):
+    np.testing.assert_array_equal(np.ascontiguousarray(a).view(np.uint16), np.ascontiguousarray(b).view(np.uint16))
+
+
+def assert_close(a, b, rtol=RTOL, atol=ATOL):
+    np.testing.assert_allclose(a.astype(np.float32), b.astype(np.float32), rtol=rtol, atol=atol)
+
+
+# ------------------------------------------------------------------------------ pack / unpack
+@pytest.mark.parametrize("name", ["w_normal", "w_unit", "w_uniform_pos", "w_edges"])
+@pytest.mark.parametrize("G", [64, 32])
+def test_quantize_golden_bit_exact(K, golden, name, G):
+    w = golden[f"q.{name}.w"]
+    q, s = K.quantize_q40(dev(w), G)
+    assert q.dtype == torch.int8 and s.dtype == torch.float16
+    assert tuple(q.shape) == golden[f"q.{name}.g{G}.packed"].shape
+    assert tuple(s.shape) == golden[f"q.{name}.g{G}.scale"].shape
+    np.testing.assert_array_equal(host(q), golden[f"q.{name}.g{G}.packed"])
+    assert_bits_equal(host(s), golden[f"q.{name}.g{G}.scale"])
+    d = K.dequantize_q40(q, s, G, w.shape, torch.float16)
+    assert_bits_equal(host(d), golden[f"q.{name}.g{G}.deq"])
+
+
+def test_dequantize_all_byte_values(K, golden):
+    b = golden["dq.bytes"]
+    d = K.triton_deq_int40(dev(b), dev(golden["dq.scale"]), 64, (b.shape[0] * 2, 64), torch.float16)
+    assert_bits_equal(host(d), golden["dq.out"])
+
+
+@pytest.mark.parametrize("G", [64, 32])
+def test_quantize_random_vs_oracle(K, G):
+    rng = np.random.default_rng(3)
+    w = (rng.standard_normal((384, 512)) * rng.choice([1e-4, 0.02, 1.0, 300.0], size=(384, 1))).astype(np.float16)
+    w[5] = 0
+    q, s = K.quantize_q40(dev(w), G)
+    qo, so = O.quantize_q40(w, G)
+    np.testing.assert_array_equal(host(q), qo)
+    assert_bits_equal(host(s), so)
+    d = K.dequantize_q40(q, s, G, w.shape, torch.float16)
+    assert_bits_equal(host(d), O.dequantize_q40(qo, so, G, w.shape))
+
+
+def test_quantize_negative_values_round_like_torch(K):
+    """The reference's Triton quantiser truncates toward zero; ours must round half-even."""
+    w = np.tile(np.array([-7, -2.5, -1.5, -0.5, 0.5, 1.5, 2.5, 7], dtype=np.float16), 16).reshape(1, 128)
+    q, s = K.triton_q_int40(dev(w), 64)
+    qo, so = O.quantize_q40(w, 64)
+    np.testing.assert_array_equal(host(q), qo)
+    codes = O.unpack_codes(host(q))
+    assert list(codes[0, :8]) == [-7, -2, -2, 0, 0, 2, 2, 7]
+
+
+def test_quantize_rows_strided_in_place(K):
+    """New-token rows of a [B, T, H*D] cache quantised into strided cache views."""
+    rng = np.random.default_rng(4)
+    Bm, T, HD = 6, 5, 512
+    x = rng.standard_normal((Bm, HD)).astype(np.float16)
+    cache_q = torch.zeros((Bm, T, HD // 2), dtype=torch.int8, device="cuda")
+    cache_s = torch.zeros((Bm, T, HD // 64), dtype=torch.float16, device="cuda")
+    t = 3
+    K.quantize_q40_rows(dev(x), cache_q[:, t], cache_s[:, t], 64)
+    qo, so = O.quantize_q40(x, 64)
+    np.testing.assert_array_equal(host(cache_q[:, t]).reshape(-1, 64), qo)
+    assert_bits_equal(host(cache_s[:, t]).reshape(-1, 1), so)
+    assert int(cache_q[:, :t].abs().sum()) == 0 and int(cache_q[:, t + 1:].abs().sum()) == 0
+
+
+def test_quantize_full_gemv_config_checksum(K, golden):
+    """4096x4096 seed-0 weight of the single-GEMV configuration: the device packer reproduces
+    the reference packer's bytes for both orientations (compared by SHA-256)."""
+    torch.manual_seed(0)
+    W = (torch.randn((4096, 4096)) * 0.02).to(torch.float16)
+    Wd = W.cuda()
+    qa, sa = K.quantize_q40(Wd, 64)
+    qb, sb = K.quantize_q40(Wd.t().contiguous(), 64)
+    got = [hashlib.sha256(host(a).tobytes()).hexdigest() for a in (qa, sa, qb, sb)]
+    assert got == list(golden["big.sha"])
+    x = dev(golden["big.x"])
+    y_kn = K.matmul_q40(x, qb, sb, (4096, 4096))
+    assert_close(host(y_kn), golden["big.y_kn"])
+    y_nk = K.linear_q40(x, qa, sa, (4096, 4096))
+    assert_close(host(y_nk), golden["big.y_nk"])
+    # round trip property at full size: dequantise -> quantise is idempotent
+    d = K.dequantize_q40(qb, sb, 64, (4096, 4096), torch.float16)
+    q2, s2 = K.quantize_q40(d, 64)
+    d2 = K.dequantize_q40(q2, s2, 64, (4096, 4096), torch.float16)
+    assert torch.equal(d.view(torch.int16), d2.view(torch.int16))
+
+
+# ------------------------------------------------------------------------------ matmul
+@pytest.mark.parametrize("M", [1, 3, 10, 17])
+def test_matmul_kn_golden(K, golden, M):
+    c = K.matmul_q40(dev(golden[f"mm.kn.m{M}.a"]), dev(golden["mm.kn.bw"]), dev(golden["mm.kn.bs"]), (256, 384))
+    assert_close(host(c), golden[f"mm.kn.m{M}.c"])
+
+
+def test_linear_nk_golden(K, golden):
+    y = K.linear_q40(dev(golden["mm.nk.x"]), dev(golden["mm.nk.wq"]), dev(golden["mm.nk.ws"]), (384, 256))
+    assert_close(host(y), golden["mm.nk.y"])
+
+
+def _rand_q(rng, rows, cols, G, std=0.02):
+    w = (rng.standard_normal((rows, cols)) * std).astype(np.float16)
+    q, s = O.quantize_q40(w, G)
+    return q, s
+
+
+@pytest.mark.parametrize("M", [1, 2, 8, 9, 16, 17, 33, 100])
+@pytest.mark.parametrize("KN", [(128, 128), (256, 384), (1024, 1152), (712, 256), (2048, 4096)])
+@pytest.mark.parametrize("G", [64, 32])
+def test_matmul_kn_vs_oracle(K, M, KN, G):
+    Kd, N = KN
+    if G == 32 and M not in (1, 10, 17):
+        pytest.skip("group 32 is covered at three batch sizes")
+    rng = np.random.default_rng(M * 1000 + Kd + N + G)
+    q, s = _rand_q(rng, Kd, N, G, std=0.5)
+    a = (rng.standard_normal((M, Kd)) * 0.5).astype(np.float16)
+    c = K.matmul_q40(dev(a), dev(q), dev(s), (Kd, N), group_size=G)
+    assert tuple(c.shape) == (M, N) and c.dtype == torch.float16
+    assert_close(host(c), O.matmul_q40(a, q, s, (Kd, N), G))
+
+
+@pytest.mark.parametrize("M", [1, 7, 16, 40])
+@pytest.mark.parametrize("NK", [(64, 128), (100, 256), (384, 1024), (4096, 2048)])
+@pytest.mark.parametrize("G", [64, 32])
+def test_linear_nk_vs_oracle(K, M, NK, G):
+    N, Kd = NK
+    rng = np.random.default_rng(M * 977 + Kd + N + G)
+    q, s = _rand_q(rng, N, Kd, G, std=0.5)
+    x = (rng.standard_normal((M, Kd)) * 0.5).astype(np.float16)
+    y = K.linear_q40(dev(x), dev(q), dev(s), (N, Kd), group_size=G)
+    assert_close(host(y), O.linear_q40_nk(x, q, s, (N, Kd), G))
+
+
+def test_matmul_7b_shapes_linearity_and_repeatability(K):
+    """Full CodeLlama-7B layer shapes: checked through properties that need no CPU matmul —
+    (a) a one-hot activation row selects exactly the dequantised weight row, (b) repeated
+    calls are bit-identical (the split-K reduction order is fixed), (c) batch rows are
+    independent of the batch they are computed in."""
+    torch.manual_seed(1)
+    for (N, Kd) in [(4096, 4096), (11008, 4096), (4096, 11008), (32128, 4096)]:
+        W = (torch.randn((Kd, N), device="cuda") * 0.02).to(torch.float16)
+        q, s = K.quantize_q40(W, 64)
+        deq = K.dequantize_q40(q, s, 64, (Kd, N), torch.float16)
+        rows = [0, 1, Kd // 2 + 3, Kd - 1]
+        a = torch.zeros((len(rows), Kd), dtype=torch.float16, device="cuda")
+        for i, r in enumerate(rows):
+            a[i, r] = 1.0
+        c = K.matmul_q40(a, q, s, (Kd, N))
+        assert torch.equal(c.view(torch.int16), deq[rows].view(torch.int16)), (N, Kd)
+        x = torch.randn((100, Kd), device="cuda", dtype=torch.float16)
+        c100 = K.matmul_q40(x, q, s, (Kd, N))
+        assert torch.equal(c100, K.matmul_q40(x, q, s, (Kd, N)))
+        c1 = K.matmul_q40(x[37:38].contiguous(), q, s, (Kd, N))
+        c10 = K.matmul_q40(x[30:40].contiguous(), q, s, (Kd, N))
+        assert torch.equal(c1[0], c100[37]) and torch.equal(c10[7], c100[37])
+        ref = (x[:4].float() @ deq.float()).to(torch.float16)
+        assert_close(host(c100[:4]), host(ref))
+
+
+# ------------------------------------------------------------------------------ attention
+def test_attn_decode_golden(K, golden):
+    q, k, v = golden["at.dec.q"], golden["at.dec.k"], golden["at.dec.v"]
+    B, H, L, D = k.shape
+    o = K.flash_attn(dev(q), dev(k), dev(v), B, L, H, D)
+    assert_close(host(o), golden["at.dec.o"])
+
+
+def test_attn_paged_golden_and_chunk(K, golden):
+    q, pager, kp, vp = golden["at.dec.q"], golden["at.pg.pager"], golden["at.pg.kp"], golden["at.pg.vp"]
+    B, L = pager.shape
+    H, P, D = kp.shape
+    o = K.page_flash_attn(dev(pager), dev(q), dev(kp), dev(vp), P, B, L, H, D)
+    assert_close(host(o), golden["at.pg.o"])
+    o2 = K.chunk_attn(dev(pager), dev(q), dev(kp), dev(vp), P, B, L, H, D, 40)
+    assert_close(host(o2), golden["at.pg.o"])
+
+
+@pytest.mark.parametrize("B,H,Hkv,L", [(1, 32, 32, 1), (3, 8, 8, 37), (100, 32, 32, 512), (4, 16, 2, 200)])
+def test_attn_decode_vs_oracle(K, B, H, Hkv, L):
+    rng = np.random.default_rng(B + L)
+    q = rng.standard_normal((B, H, 128)).astype(np.float16)
+    k = rng.standard_normal((B, Hkv, L, 128)).astype(np.float16)
+    v = rng.standard_normal((B, Hkv, L, 128)).astype(np.float16)
+    o = K.flash_attn(dev(q), dev(k), dev(v), B, L, H, 128)
+    if B * H * L > 200000:   # the python-loop oracle is slow: check a subset of branches
+        idx = [0, B // 2, B - 1]
+        assert_close(host(o)[idx], O.attn_decode(q[idx], k[idx], v[idx]))
+    else:
+        assert_close(host(o), O.attn_decode(q, k, v))
+
+
+def _paged_case(rng, B, H, Hkv, lens, page_size, idx_dtype):
+    n_pages = [(l + page_size - 1) // page_size for l in lens]
+    total_pages = sum(n_pages) + 3
+    P = total_pages * page_size
+    perm = rng.permutation(total_pages)
+    tbl = np.zeros((B, max(max(n_pages), 1)), dtype=idx_dtype)
+    c = 0
+    for b in range(B):
+        tbl[b, : n_pages[b]] = perm[c: c + n_pages[b]]
+        c += n_pages[b]
+    kp = rng.standard_normal((Hkv, P, 128)).astype(np.float16)
+    vp = rng.standard_normal((Hkv, P, 128)).astype(np.float16)
+    q = rng.standard_normal((B, H, 128)).astype(np.float16)
+    return q, tbl, kp, vp, P
+
+
+@pytest.mark.parametrize("page_size,idx", [(1, np.int16), (16, np.int32), (16, np.int16), (8, np.int32)])
+def test_attn_paged_ragged_vs_oracle(K, page_size, idx):
+    rng = np.random.default_rng(page_size)
+    lens = [0, 1, 15, 16, 17, 100, 256]
+    B, H, Hkv = len(lens), 8, 4
+    q, tbl, kp, vp, P = _paged_case(rng, B, H, Hkv, lens, page_size, idx)
+    sl = np.array(lens, dtype=np.int32)
+    o = K.page_flash_attn(dev(tbl), dev(q), dev(kp), dev(vp), P, B, max(lens), H, 128,
+                          page_size=page_size, seq_lens=dev(sl))
+    ref = O.attn_paged(tbl, sl, q, kp, vp, page_size)
+    assert_close(host(o), ref)
+    assert float(host(o)[0].astype(np.float32).max()) == 0.0   # empty branch -> zeros
+
+
+@pytest.mark.parametrize("B,H,Hkv,prefix", [(5, 4, 4, 40), (64, 8, 8, 300), (100, 4, 4, 129), (9, 16, 2, 64),
+                                            (1, 32, 32, 2048)])
+def test_attn_shared_prefix_vs_oracle(K, B, H, Hkv, prefix):
+    rng = np.random.default_rng(B * 7 + prefix)
+    lens = list(rng.integers(0, 70, size=B))
+    lens[0] = 0
+    q, tbl, kp, vp, P = _paged_case(rng, B, H, Hkv, lens, 16, np.int32)
+    pk = rng.standard_normal((prefix + 5, Hkv, 128)).astype(np.float16)
+    pv = rng.standard_normal((prefix + 5, Hkv, 128)).astype(np.float16)
+    sl = np.array(lens, dtype=np.int32)
+    o = K.shared_prefix_attn(dev(q), dev(pk), dev(pv), prefix, dev(tbl), dev(sl), dev(kp), dev(vp), page_size=16)
+    sub = list(range(B)) if B * H * prefix < 400000 else [0, 1, B // 2, B - 1]
+    ref = O.attn_shared_prefix(q[sub], pk, pv, prefix, tbl[sub], sl[sub], kp, vp, 16)
+    assert_close(host(o)[sub], ref)
+    # property at any size: shared-prefix result == paged attention over an explicit table that lists
+    # the prefix slots first (the reference's representation)
+    if Hkv == H and B <= 64:
+        ppool_k = np.concatenate((pk[:prefix].transpose(1, 0, 2), kp), axis=1)
+        ppool_v = np.concatenate((pv[:prefix].transpose(1, 0, 2), vp), axis=1)
+        Lmax = prefix + max(lens)
+        full = np.zeros((B, Lmax), dtype=np.int32)
+        for b in range(B):
+            full[b, :prefix] = np.arange(prefix)
+            t = np.arange(lens[b])
+            full[b, prefix: prefix + lens[b]] = prefix + tbl[b, t // 16] * 16 + t % 16
+        o2 = K.page_flash_attn(dev(full), dev(q), dev(ppool_k), dev(ppool_v), ppool_k.shape[1], B, Lmax, H, 128,
+                               seq_lens=dev(sl + prefix))
+        assert_close(host(o), host(o2), rtol=1e-2, atol=2e-3)
+
+
+def test_attn_shared_prefix_config3_geometry(K):
+    """32 heads, head_dim 128, prefix 2048, 64 branches with suffix lengths U[0,256] in 16-token
+    pages: compared with the unshared paged kernel and, for three branches, the oracle."""
+    rng = np.random.default_rng(0)
+    B, H, prefix = 64, 32, 2048
+    lens = list(rng.integers(0, 257, size=B))
+    q, tbl, kp, vp, P = _paged_case(rng, B, H, H, lens, 16, np.int32)
+    pk = rng.standard_normal((prefix, H, 128)).astype(np.float16)
+    pv = rng.standard_normal((prefix, H, 128)).astype(np.float16)
+    sl = np.array(lens, dtype=np.int32)
+    o = K.shared_prefix_attn(dev(q), dev(pk), dev(pv), prefix, dev(tbl), dev(sl), dev(kp), dev(vp), page_size=16)
+    sub = [0, 31, 63]
+    ref = O.attn_shared_prefix(q[sub], pk, pv, prefix, tbl[sub], sl[sub], kp, vp, 16)
+    assert_close(host(o)[sub], ref)
+
+
+def test_triton_attn_wrapper(K):
+    rng = np.random.default_rng(5)
+    q = (rng.standard_normal((1, 4, 20, 128)) * 0.5).astype(np.float16)
+    k = (rng.standard_normal((1, 4, 96, 128)) * 0.5).astype(np.float16)
+    v = (rng.standard_normal((1, 4, 96, 128)) * 0.5).astype(np.float16)
+    o = K.triton_attn(dev(q), dev(k), dev(v), False, 1.0 / np.sqrt(128))
+    ref = torch.nn.functional.scaled_dot_product_attention(
+        torch.from_numpy(q).float(), torch.from_numpy(k).float(), torch.from_numpy(v).float())
+    assert_close(host(o), ref.numpy().astype(np.float16))
+
+
+# ------------------------------------------------------------------------------ epilogues
+def test_rmsnorm_golden(K, golden):
+    y = K.rmsnorm(dev(golden["ep.rms.x"]), dev(golden["ep.rms.w"]), 1e-5)
+    d = np.abs(host(y).view(np.int16).astype(np.int32) - golden["ep.rms.y"].view(np.int16).astype(np.int32))
+    assert d.max() <= 1 and (d > 0).mean() < 0.01
+
+
+def test_rmsnorm_residual(K):
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal((5, 4096)).astype(np.float16)
+    r = rng.standard_normal((5, 4096)).astype(np.float16)
+    w = (1 + 0.1 * rng.standard_normal(4096)).astype(np.float16)
+    y, h = K.rmsnorm(dev(x), dev(w), 1e-5, residual=dev(r))
+    href = (x.astype(np.float32) + r.astype(np.float32)).astype(np.float16)
+    assert_bits_equal(host(h), href)
+    yref = O.rmsnorm(href, w, 1e-5)
+    d = np.abs(host(y).view(np.int16).astype(np.int32) - yref.view(np.int16).astype(np.int32))
+    assert d.max() <= 1 and (d > 0).mean() < 0.01
+
+
+def test_rope_golden_bit_exact(K, golden):
+    pos = int(golden["ep.rope.pos"])
+    cos, sin = dev(golden["ep.rope.cos"]), dev(golden["ep.rope.sin"])
+    for name in ("q", "k"):
+        x = dev(golden[f"ep.rope.{name}"]).view(3, 4, 128).clone()
+        K.rope_(x, torch.full((3,), pos, dtype=torch.int32, device="cuda"), cos, sin)
+        assert_bits_equal(host(x).reshape(3, 1, 4, 128), golden[f"ep.rope.o{name}"])
+
+
+def test_silu_mul_golden(K, golden):
+    y = K.silu_mul(dev(golden["ep.silu.a"]), dev(golden["ep.silu.b"]))
+    d = np.abs(host(y).view(np.int16).astype(np.int32) - golden["ep.silu.y"].view(np.int16).astype(np.int32))
+    assert d.max() <= 1 and (d > 0).mean() < 0.01
