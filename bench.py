@@ -1,0 +1,384 @@
+#!/usr/bin/env python
+"""Benchmark of the Q4_0 decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N = 1): CodeLlama-7B-architecture Q4_0 decode with random-init weights — 32
+layers, hidden 4096, 32 heads, head_dim 128, FFN 11008, vocab 32016, weights N(0, 0.02^2)
+quantised to Q4_0 (group 64), norm weights 1, prompt of 512 uniform-random token ids shared
+by all branches, then greedy decode steps at tree width 1 (headline), 10 and 100.
+A "step" is one decode step of all `width` branches; value = width * steps / time.
+
+Printed line (rank 0): the driver's JSON contract, plus
+  roofline      the fused dequant-matmul kernel on the model's own 224 weight matrices
+                (larger than L2, streamed in layer order), algorithmic bytes / CUDA-event time
+  cpu_baseline  the reference's CPU path (torch unpack + matmul) on the host cores, bounded
+                sample: the 7 linears of one layer, extrapolated to a token
+  e2e           the same metric through model(tokens, start_pos) with host tokens in pinned
+                memory copied in and the argmax token ids copied out every step
+With N > 1 the 7B path does not shard: every rank runs an independent replica
+(scaling "weak"), value is the sum over replicas divided by the slowest replica's time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+PROMPT_LEN = 512
+WIDTHS = (1, 10, 100)
+MAX_SEQ = 256
+METRIC = "q4_0_decode_tokens_per_s_7b_batch1"
+UNIT = "tokens/s"
+N_LAYERS, DIM, HEADS, FFN, VOCAB = 32, 4096, 32, 11008, 32016
+LAYER_SHAPES = [(4096, 4096)] * 4 + [(11008, 4096), (11008, 4096), (4096, 11008)]   # (N, K): q k v o w1 w3 w2
+
+
+def q4_bytes(n, k, m, group=64):
+    """Algorithmic bytes of one fused dequant-matmul: packed weight + scales + A + C."""
+    return n * k // 2 + n * k // group * 2 + 2 * m * k + 2 * m * n
+
+
+def step_weight_bytes():
+    return N_LAYERS * sum(n * k // 2 + n * k // 64 * 2 for n, k in LAYER_SHAPES) + VOCAB * DIM * 2
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        self.t.join(timeout=2)
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0])); mx = float(f[1])
+            except ValueError:
+                continue
+            for nm, val in zip(names, f[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_layer_sample(width, threads, repeats):
+    """Time the reference's CPU path on the 7 Q4_0 linears of one 7B layer at batch `width`.
+    Returns seconds per layer (median over repeats) and the unpack/matmul split."""
+    import torch
+    from oracle import cpu_path as C
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    mats = []
+    for (n, k) in sorted(set(LAYER_SHAPES)):
+        wt = (torch.randn((k, n), generator=g) * 0.02).to(torch.float16)
+        q, s = C.quantize(wt, 64)
+        mats.append(((n, k), q, s))
+    by_shape = {m[0]: m for m in mats}
+    xs = {k: torch.randn((width, k), generator=g).to(torch.float16) for k in (4096, 11008)}
+    times, deq_t, mm_t = [], 0.0, 0.0
+    for r in range(repeats + 1):
+        t0 = time.perf_counter()
+        d_acc = m_acc = 0.0
+        for (n, k) in LAYER_SHAPES:
+            _, q, s = by_shape[(n, k)]
+            _, td, tm = C.linear_kn(xs[k], q, s, (k, n))
+            d_acc += td; m_acc += tm
+        if r > 0:       # first pass is the warm-up
+            times.append(time.perf_counter() - t0); deq_t += d_acc; mm_t += m_acc
+    times.sort()
+    return times[len(times) // 2], deq_t / repeats, mm_t / repeats
+
+
+def run_reference_arm(args):
+    """`--impl reference`: the reference's own CPU implementation of the path (restated in
+    oracle/cpu_path.py; the reference is Python and does not travel to the GPU box), all host
+    threads.  One step = the Q4_0 linears of one layer at batch 1; tokens/s extrapolates
+    to 32 layers (attention, norms and the fp16 lm_head are left out, which favours the CPU)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    steps, warm = max(args.steps, 1), max(args.warmup, 0)
+    steps = min(steps, 20)          # bounded: one step is ~0.3-1 s of CPU work
+    t_layer, td, tm = cpu_layer_sample(1, threads, steps)
+    value = 1.0 / (t_layer * N_LAYERS)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": 1, "ms_per_step": t_layer * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "codellama-7b-arch q4_0 decode, width 1, prompt 512 (CPU: linears of one layer per step, x32)",
+                   "group": 64},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": "7 Q4_0 linears of one layer (torch unpack + matmul), median of %d, x32 layers; "
+                                   "unpack %.1f ms + matmul %.1f ms per layer" % (steps, td * 1e3, tm * 1e3)},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def build_model(device):
+    import torch
+    from spec_mcts_b200.model import ModelArgs, Transformer, random_init_
+    args = ModelArgs(dim=DIM, n_layers=N_LAYERS, n_heads=HEADS, vocab_size=VOCAB, multiple_of=256,
+                     max_batch_size=max(WIDTHS), max_seq_len=MAX_SEQ, max_prompt_seq_len=PROMPT_LEN)
+    model = Transformer(args, device=device)
+    random_init_(model, seed=0)
+    model = model.to(device, torch.float16)
+    return model
+
+
+def timed_decode(model, width, steps, warmup, prompt_len):
+    """Device-resident greedy decode: tokens and positions are fed back on the device inside
+    the captured step; K replays are timed with CUDA events."""
+    import torch
+    dev = model.device
+    model.greedy_feedback = True
+    model._pos_dev[:width].fill_(prompt_len)
+    model._tok_dev[:width].copy_(torch.arange(width, device=dev) % VOCAB)
+    for _ in range(warmup):
+        model.decode_replay(width)
+        _wrap(model, width, prompt_len)
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        model.decode_replay(width)
+        _wrap(model, width, prompt_len)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    model.greedy_feedback = False
+    return e0.elapsed_time(e1) * 1e-3
+
+
+_step_no = {}
+
+
+def _wrap(model, width, prompt_len):
+    """Keep the position inside the suffix cache when more steps are run than it holds."""
+    n = _step_no.get(width, 0) + 1
+    _step_no[width] = n
+    if n % (MAX_SEQ - 1) == 0:
+        model._pos_dev[:width].fill_(prompt_len)
+
+
+def timed_e2e(model, width, steps, warmup, prompt_len):
+    """Through the public call model(tokens, start_pos): host tokens (pinned) in, argmax token
+    ids out, every step."""
+    import torch
+    dev = model.device
+    tok_host = torch.zeros((width, 1), dtype=torch.int64).pin_memory()
+    out_host = torch.zeros((width,), dtype=torch.int64).pin_memory()
+    tok_host[:, 0] = torch.arange(width) % VOCAB
+    pos = prompt_len
+
+    def one():
+        nonlocal pos
+        logits = model(tok_host.to(dev, non_blocking=True), pos)
+        out_host.copy_(logits[:, -1].argmax(dim=-1), non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()      # the next step's input is this result
+        tok_host[:, 0] = out_host
+        pos += 1
+        if pos - prompt_len >= MAX_SEQ - 1:
+            pos = prompt_len
+
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        one()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    return e0.elapsed_time(e1) * 1e-3, width * 8, width * 8
+
+
+def gemv_roofline(model, width, reps):
+    """The dominant kernel alone: every Q4_0 linear of the model in layer order (3.4 GB of
+    distinct weights per pass, so nothing is served from L2), CUDA events around the passes."""
+    import torch
+    from spec_mcts_b200._lib import check, lib
+    dev = model.device
+    st = torch.cuda.current_stream(dev).cuda_stream
+    lins = []
+    for layer in model.layers:
+        a, f = layer.attention, layer.feed_forward
+        lins += [a.wq, a.wk, a.wv, a.wo, f.w1, f.w3, f.w2]
+    xs = {k: torch.randn((width, k), device=dev, dtype=torch.float16) for k in (DIM, FFN)}
+    outs = {n: torch.empty((width, n), device=dev, dtype=torch.float16) for n in (DIM, FFN)}
+    ws = torch.zeros(max(lib.q40_gemm_workspace_bytes(width, n, k) for n, k in LAYER_SHAPES), dtype=torch.uint8,
+                     device=dev)
+
+    def one_pass():
+        for lin in lins:
+            k, n = lin.kn()
+            check(lib.q40_gemm_kn(xs[k].data_ptr(), k, lin.w.data_ptr(), lin.s.data_ptr(), outs[n].data_ptr(), n,
+                                  width, n, k, 64, ws.data_ptr(), ws.numel(), st))
+    for _ in range(3):
+        one_pass()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        one_pass()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    sec = e0.elapsed_time(e1) * 1e-3
+    launches = reps * len(lins) * ((width + 15) // 16)
+    total_bytes = reps * sum(q4_bytes(lin.kn()[1], lin.kn()[0], width) for lin in lins)
+    return total_bytes / sec / 1e9, sec / launches, total_bytes / launches
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--widths", default=",".join(str(w) for w in WIDTHS))
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the q40b200 kernels have no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    widths = [int(w) for w in args.widths.split(",")]
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
+
+    model = build_model(dev)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, VOCAB, (1, PROMPT_LEN), generator=g)
+    with torch.inference_mode():
+        model(prompt.to(dev), 0)
+        model.fork(0, 1, max(widths) - 1)
+        torch.cuda.synchronize(dev)
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize(dev)
+
+        sampler = ClockSampler(local_rank)
+        results, e2e_res = {}, {}
+        barrier()
+        if rank == 0:
+            sampler.start()
+        for w in widths:
+            barrier()
+            sec = timed_decode(model, w, steps, warmup, PROMPT_LEN)
+            barrier()
+            if world > 1:
+                t = torch.tensor([sec], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                sec = float(t.item())
+            results[w] = sec
+        clocks = sampler.stop() if rank == 0 else None
+        for w in widths:
+            barrier()
+            sec, h2d, d2h = timed_e2e(model, w, steps, warmup, PROMPT_LEN)
+            if world > 1:
+                t = torch.tensor([sec], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                sec = float(t.item())
+            e2e_res[w] = (sec, h2d, d2h)
+        roof = gemv_roofline(model, widths[0], reps=5) if rank == 0 else None
+
+    if rank == 0:
+        w0 = widths[0]
+        tok_s = {w: world * w * steps / results[w] for w in widths}
+        e2e_tok_s = {w: world * w * steps / e2e_res[w][0] for w in widths}
+        ach, sec_per_launch, bytes_per_launch = roof
+        step_bytes = step_weight_bytes()
+        line = {
+            "metric": METRIC, "value": tok_s[w0], "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": results[w0] / steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "codellama-7b-arch q4_0 decode (32 layers, hidden 4096, ffn 11008, vocab 32016), "
+                                   "random-init N(0,0.02^2) weights, prompt 512 shared, greedy, width %d" % w0,
+                       "group": 64, "prompt_len": PROMPT_LEN, "widths": widths, "replicas": world,
+                       "l2": "inputs larger than L2 (3.7 GB of weights streamed per step)"},
+            "by_width": {str(w): {"tokens_per_s": tok_s[w], "ms_per_step": results[w] / steps * 1e3,
+                                  "e2e_tokens_per_s": e2e_tok_s[w]} for w in widths},
+            "step_weight_stream": {"bytes_per_step": step_bytes,
+                                   "achieved_gbs": step_bytes / (results[w0] / steps) / 1e9,
+                                   "frac_of_%s_hbm" % peak_kind: step_bytes / (results[w0] / steps) / 1e9 / hbm_peak},
+            "roofline": {"bound": "hbm", "kernel": "gemv_kn_kernel<64,1>", "achieved": ach, "peak": hbm_peak,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": ach / hbm_peak,
+                         "avg_launch_us": sec_per_launch * 1e6, "alg_bytes_per_launch": bytes_per_launch,
+                         "traffic": None},
+            "e2e": {"value": e2e_tok_s[w0], "unit": UNIT, "h2d_bytes_per_step": e2e_res[w0][1],
+                    "d2h_bytes_per_step": e2e_res[w0][2]},
+            "gpu_launches": steps * model.launches_per_step,
+            "clocks": clocks,
+        }
+        if not args.no_cpu and world == 1:
+            threads = os.cpu_count() or 1
+            t_layer, td, tm = cpu_layer_sample(1, threads, 5)
+            line["cpu_baseline"] = {"value": 1.0 / (t_layer * N_LAYERS), "unit": UNIT, "cores": threads, "kind": "port",
+                                    "sample": "7 Q4_0 linears of one layer at batch 1 (torch unpack %.1f ms + matmul "
+                                              "%.1f ms), median of 5, x32 layers; attention/norms/lm_head not counted"
+                                              % (td * 1e3, tm * 1e3)}
+        else:
+            line["cpu_baseline"] = None
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -124,6 +124,36 @@ int q40_attn_shared_prefix(const void* q, const void* prefix_k, const void* pref
                            int D, int page_size, void* workspace, size_t workspace_bytes,
                            void* stream);
 
+/* One decode step of the KV-shared model's attention, replayable from a CUDA graph because
+ * every length is read from device memory: all B branches attend to the shared fp16 prompt
+ * cache (first *prefix_len_dev <= max_prefix_len keys), then to their own Q4_0 suffix cache
+ * (packed rows cache_kq/cache_vq [maxB, max_t, Hkv, 64] bytes with scales cache_ks/cache_vs
+ * [maxB, max_t, Hkv, 2] fp16; branch b holds pos_dev[b] - *prefix_len_dev tokens), and
+ * finally, if cur_k/cur_v are given, to the un-quantised K/V of the token being decoded
+ * (rows of cur_stride elements, [B, Hkv*D]).  Workspace as q40_attn_shared_prefix sized for
+ * max_prefix_len.
+ * Replaces: the decode branch of Attention.forward (hf_model_q40_kv_shared.py:330-405):
+ * dequantise the whole suffix, overwrite the new position, cat with the expanded prompt, SDPA. */
+int q40_attn_tree_decode(const void* q, const void* prefix_k, const void* prefix_v,
+                         int max_prefix_len, const int32_t* prefix_len_dev,
+                         int64_t prefix_key_stride, int64_t prefix_head_stride,
+                         const void* cache_kq, const void* cache_ks, const void* cache_vq,
+                         const void* cache_vs, int max_t, const int32_t* pos_dev, const void* cur_k,
+                         const void* cur_v, int64_t cur_stride, void* o, int B, int H, int Hkv, int D,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* Rotary embedding of the new token's q [B, H*D] and k [B, Hkv*D] in place (position
+ * pos_dev[b], tables cos/sin [n_pos, D/2] fp16) and Q4_0 append of the rotated k and of v to
+ * the suffix cache at slot (b, pos_dev[b] - *prefix_len_dev); k and v stay un-quantised in
+ * their buffers for this step's attention.  Strides in elements.  D == 128.
+ * Replaces: apply_rotary_emb (hf_model_q40_kv_shared.py:166-203, 317) and the quantise-and-
+ * store of the new rows (:365-371). */
+int q40_rope_kv_append(void* q, int64_t q_stride, void* k, int64_t k_stride, const void* v,
+                       int64_t v_stride, const int32_t* pos_dev, const int32_t* prefix_len_dev,
+                       const void* cos_tbl, const void* sin_tbl, int n_pos, void* cache_kq,
+                       void* cache_ks, void* cache_vq, void* cache_vs, int B, int H, int Hkv, int D,
+                       int max_t, void* stream);
+
 /* ---- epilogue math with the reference's rounding points ------------------------------ */
 
 /* y[r,:] = fp16(fp16(x32 * rsqrt(mean(x32^2) + eps)) * w); if `residual` is non-NULL the

@@ -15,14 +15,17 @@ _LIB_PATH = _build.LIB
 
 
 def _load() -> ctypes.CDLL:
-    if not os.path.exists(_LIB_PATH):
-        # a source checkout without the built library: compile it (needs nvcc)
+    if _build.needs_build():
+        # missing, or older than a source file: compile it in place (needs nvcc)
         try:
             _build.build()
         except Exception as e:  # pragma: no cover - depends on the toolchain
-            raise ImportError(
-                f"libq40b200.so is not built and building it failed: {e}\n"
-                "run `python -m spec_mcts_b200.build` on a machine with nvcc 12.8+") from e
+            if not os.path.exists(_LIB_PATH):
+                raise ImportError(
+                    f"libq40b200.so is not built and building it failed: {e}\n"
+                    "run `python -m spec_mcts_b200.build` on a machine with nvcc 12.8+") from e
+            import warnings
+            warnings.warn(f"libq40b200.so is older than its sources and rebuilding failed: {e}")
     return ctypes.CDLL(_LIB_PATH)
 
 
@@ -49,6 +52,13 @@ SIGNATURES = {
     "q40_attn_shared_prefix": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64,
                                        c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                        c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "q40_attn_tree_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                     c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                     c_size_t, c_void_p]),
+    "q40_rope_kv_append": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
+                                   c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "q40_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
                             c_void_p]),
     "q40_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64,

@@ -24,7 +24,7 @@ constexpr int BR_UNROLL = 4;                // keys per group per iteration
 
 template <int MODE>  // 0 contiguous, 1 paged with int16 ids, 2 paged with int32 ids
 __device__ __forceinline__ int64_t key_slot(const BranchArgs& a, int b, int hk, int t) {
-  if (MODE == 0) {
+  if (MODE == 0 || MODE == 3) {
     return ((int64_t)(b * a.Hkv + hk) * a.L + t);
   } else {
     const int pg = t / a.page_size, in = t - pg * a.page_size;
@@ -50,7 +50,9 @@ attn_branch_kernel(const BranchArgs a) {
   const int hk = h / (a.H / a.Hkv);
   const int tid = threadIdx.x, lane = tid & 31;
   const int grp = tid >> 3, sub = tid & 7;
-  const int len = a.seq_lens ? min(max(a.seq_lens[b], 0), a.L) : a.L;
+  int len;
+  if (MODE == 3) len = min(max(a.pos[b] - a.prefix_len[0], 0), a.max_t);
+  else len = a.seq_lens ? min(max(a.seq_lens[b], 0), a.L) : a.L;
 
   __shared__ float sm_m[BR_GROUPS], sm_l[BR_GROUPS];
   __shared__ __align__(16) float sm_o[BR_GROUPS][D];
@@ -76,6 +78,7 @@ attn_branch_kernel(const BranchArgs a) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) o[i] = 0.f;
 
+  if (MODE != 3)
   for (int t0 = grp; t0 < len; t0 += BR_GROUPS * BR_UNROLL) {
     uint4 kv[BR_UNROLL][4];
     float s[BR_UNROLL];
@@ -129,6 +132,110 @@ attn_branch_kernel(const BranchArgs a) {
     m = mnew;
   }
 
+  if (MODE == 3) {
+    // Q4_0 cache: lane `sub` owns dims 16*sub..16*sub+15 = nibble half (sub>>2) of bytes 16*(sub&3)..+15
+    const int nib_lo = sub >> 2;                 // 0: high nibbles (dims 0..63), 1: low nibbles
+    const int boff = 16 * (sub & 3);
+    for (int t0 = grp; t0 < len; t0 += BR_GROUPS * BR_UNROLL) {
+      uint4 kb[BR_UNROLL], vb[BR_UNROLL];
+      __half ksv[BR_UNROLL], vsv[BR_UNROLL];
+      float s[BR_UNROLL];
+#pragma unroll
+      for (int u = 0; u < BR_UNROLL; ++u) {
+        const int t = t0 + u * BR_GROUPS;
+        if (t < len) {
+          const int64_t row = ((int64_t)b * a.max_t + t) * a.Hkv + hk;
+          kb[u] = __ldg(reinterpret_cast<const uint4*>(a.kq + row * 64 + boff));
+          vb[u] = __ldg(reinterpret_cast<const uint4*>(a.vq + row * 64 + boff));
+          ksv[u] = a.ksc[row * 2 + nib_lo];
+          vsv[u] = a.vsc[row * 2 + nib_lo];
+        } else {
+          kb[u] = vb[u] = make_uint4(0, 0, 0, 0);
+          ksv[u] = vsv[u] = __float2half(0.f);
+        }
+      }
+      float mnew = m;
+#pragma unroll
+      for (int u = 0; u < BR_UNROLL; ++u) {
+        const uint32_t* wd = reinterpret_cast<const uint32_t*>(&kb[u]);
+        const __half2 sc = __half2half2(ksv[u]);
+        float acc = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+          const uint32_t w = nib_lo ? wd[wi] : (wd[wi] >> 4);
+          const float2 f02 = __half22float2(__hmul2(codes_lo_to_h2(w), sc));        // bytes 0, 2
+          const float2 f13 = __half22float2(__hmul2(codes_lo_to_h2(w >> 8), sc));   // bytes 1, 3
+          acc = fmaf(qf[4 * wi + 0], f02.x, acc);
+          acc = fmaf(qf[4 * wi + 2], f02.y, acc);
+          acc = fmaf(qf[4 * wi + 1], f13.x, acc);
+          acc = fmaf(qf[4 * wi + 3], f13.y, acc);
+        }
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+        s[u] = (t0 + u * BR_GROUPS < len) ? acc : -CUDART_INF_F;
+        mnew = fmaxf(mnew, s[u]);
+      }
+      const float corr = exp2f(m - mnew);
+      l *= corr;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) o[i] *= corr;
+#pragma unroll
+      for (int u = 0; u < BR_UNROLL; ++u) {
+        const float p = exp2f(s[u] - mnew);
+        l += p;
+        const uint32_t* wd = reinterpret_cast<const uint32_t*>(&vb[u]);
+        const __half2 sc = __half2half2(vsv[u]);
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+          const uint32_t w = nib_lo ? wd[wi] : (wd[wi] >> 4);
+          const float2 f02 = __half22float2(__hmul2(codes_lo_to_h2(w), sc));
+          const float2 f13 = __half22float2(__hmul2(codes_lo_to_h2(w >> 8), sc));
+          o[4 * wi + 0] = fmaf(p, f02.x, o[4 * wi + 0]);
+          o[4 * wi + 2] = fmaf(p, f02.y, o[4 * wi + 2]);
+          o[4 * wi + 1] = fmaf(p, f13.x, o[4 * wi + 1]);
+          o[4 * wi + 3] = fmaf(p, f13.y, o[4 * wi + 3]);
+        }
+      }
+      m = mnew;
+    }
+  }
+  // the token being decoded attends to its own, un-quantised K/V: one extra key for group 0
+  if (a.cur_k != nullptr && grp == 0) {
+    const __half* kp = a.cur_k + (int64_t)b * a.cur_stride + hk * D + sub * 16;
+    const __half* vp = a.cur_v + (int64_t)b * a.cur_stride + hk * D + sub * 16;
+    const uint4 k0 = *reinterpret_cast<const uint4*>(kp), k1 = *reinterpret_cast<const uint4*>(kp + 8);
+    const uint4 v0 = *reinterpret_cast<const uint4*>(vp), v1 = *reinterpret_cast<const uint4*>(vp + 8);
+    const __half2* kh0 = reinterpret_cast<const __half2*>(&k0);
+    const __half2* kh1 = reinterpret_cast<const __half2*>(&k1);
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f0 = __half22float2(kh0[i]), f1 = __half22float2(kh1[i]);
+      acc = fmaf(qf[2 * i], f0.x, acc);
+      acc = fmaf(qf[2 * i + 1], f0.y, acc);
+      acc = fmaf(qf[8 + 2 * i], f1.x, acc);
+      acc = fmaf(qf[8 + 2 * i + 1], f1.y, acc);
+    }
+    acc += __shfl_xor_sync(0x000000ffu, acc, 1);
+    acc += __shfl_xor_sync(0x000000ffu, acc, 2);
+    acc += __shfl_xor_sync(0x000000ffu, acc, 4);
+    const float mnew = fmaxf(m, acc);
+    const float corr = exp2f(m - mnew), p = exp2f(acc - mnew);
+    l = l * corr + p;
+    const __half2* vh0 = reinterpret_cast<const __half2*>(&v0);
+    const __half2* vh1 = reinterpret_cast<const __half2*>(&v1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f0 = __half22float2(vh0[i]), f1 = __half22float2(vh1[i]);
+      o[2 * i] = fmaf(p, f0.x, o[2 * i] * corr);
+      o[2 * i + 1] = fmaf(p, f0.y, o[2 * i + 1] * corr);
+      o[8 + 2 * i] = fmaf(p, f1.x, o[8 + 2 * i] * corr);
+      o[8 + 2 * i + 1] = fmaf(p, f1.y, o[8 + 2 * i + 1] * corr);
+    }
+    m = mnew;
+  }
+
   if (sub == 0) { sm_m[grp] = m; sm_l[grp] = l; }
 #pragma unroll
   for (int i = 0; i < 16; i += 4)
@@ -166,7 +273,8 @@ int launch_branch(const BranchArgs& a, int mode, int B, cudaStream_t st) {
   const unsigned grid = (unsigned)(B * a.H);
   if (mode == 0) attn_branch_kernel<0><<<grid, BR_THREADS, 0, st>>>(a);
   else if (mode == 1) attn_branch_kernel<1><<<grid, BR_THREADS, 0, st>>>(a);
-  else attn_branch_kernel<2><<<grid, BR_THREADS, 0, st>>>(a);
+  else if (mode == 2) attn_branch_kernel<2><<<grid, BR_THREADS, 0, st>>>(a);
+  else attn_branch_kernel<3><<<grid, BR_THREADS, 0, st>>>(a);
   Q40_LAUNCH_CHECK();
   return Q40_OK;
 }

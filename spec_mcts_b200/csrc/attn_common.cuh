@@ -23,9 +23,22 @@ struct BranchArgs {
   const float* po;        // [nsp][B*H][128]
   int nsp;
   float scale_log2;       // 1/sqrt(D) * log2(e)
+  // Q4_0 suffix cache (mode 3): packed rows [B, max_t, Hkv, 64] + scales [B, max_t, Hkv, 2];
+  // the branch's suffix length is pos[b] - prefix_len[0] (device values)
+  const int8_t* kq;
+  const __half* ksc;
+  const int8_t* vq;
+  const __half* vsc;
+  const int32_t* pos;
+  const int32_t* prefix_len;
+  int max_t;
+  // optional un-quantised K/V of the token being decoded, [B, Hkv*D] rows of stride cur_stride
+  const __half* cur_k;
+  const __half* cur_v;
+  int64_t cur_stride;
 };
 
-// defined in attn_branch.cu; mode 0 contiguous, 1 paged/int16 ids, 2 paged/int32 ids
+// defined in attn_branch.cu; mode 0 contiguous, 1 paged/int16 ids, 2 paged/int32 ids, 3 Q4_0 cache
 int launch_branch(const BranchArgs& a, int mode, int B, cudaStream_t st);
 
 }  // namespace q40

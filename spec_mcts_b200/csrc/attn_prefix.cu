@@ -32,6 +32,7 @@ struct PrefixArgs {
   float* pl;
   float* po;          // [nsp][B*H][D]
   int64_t key_stride, head_stride;   // elements between consecutive keys / kv heads of pk, pv
+  const int32_t* prefix_len_dev;     // optional device scalar overriding prefix_len (<= prefix_len)
   int B, H, Hkv, prefix_len, keys_per_split;
   float scale_log2;
 };
@@ -90,8 +91,9 @@ attn_prefix_kernel(const PrefixArgs a) {
   const int rep = a.H / a.Hkv;
   const int rows = a.B * rep;                 // query rows of this kv head
   const int row0 = rblk * RB;
+  const int plen = a.prefix_len_dev ? min(max(a.prefix_len_dev[0], 0), a.prefix_len) : a.prefix_len;
   const int k_begin = sp * a.keys_per_split;
-  const int k_end = min(a.prefix_len, k_begin + a.keys_per_split);
+  const int k_end = min(plen, k_begin + a.keys_per_split);
   const int ntiles = (k_end > k_begin) ? (k_end - k_begin + PF_KT - 1) / PF_KT : 0;
 
   // ---- Q rows -> shared (swizzled) -> A fragments in registers ----
@@ -260,6 +262,25 @@ static int prefix_splits(int B, int H, int Hkv, int prefix_len) {
   return (tiles + tiles_per - 1) / tiles_per;               // every split is non-empty
 }
 
+// pa.prefix_len is the (maximum) prefix length the grid is sized for
+static int launch_prefix(PrefixArgs& pa, int nsp, cudaStream_t st) {
+  const int tiles = (pa.prefix_len + PF_KT - 1) / PF_KT;
+  pa.keys_per_split = ((tiles + nsp - 1) / nsp) * PF_KT;
+  const int rep = pa.H / pa.Hkv, rows = pa.B * rep;
+  const size_t smem = 4 * PF_TILE_BYTES;  // two stages of K and V (also covers 128 staged Q rows)
+  if (rows <= 64) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefix_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attn_prefix_kernel<4><<<dim3(nsp, pa.Hkv, 1), 128, smem, st>>>(pa);
+  } else {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefix_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attn_prefix_kernel<8><<<dim3(nsp, pa.Hkv, (rows + 127) / 128), 256, smem, st>>>(pa);
+  }
+  Q40_LAUNCH_CHECK();
+  return Q40_OK;
+}
+
 }  // namespace q40
 
 extern "C" size_t q40_attn_shared_prefix_workspace_bytes(int B, int H, int D, int prefix_len) {
@@ -313,25 +334,62 @@ extern "C" int q40_attn_shared_prefix(const void* q, const void* prefix_k, const
     pa.pm = pm; pa.pl = pl; pa.po = po;
     pa.key_stride = prefix_key_stride; pa.head_stride = prefix_head_stride;
     pa.B = B; pa.H = H; pa.Hkv = Hkv; pa.prefix_len = prefix_len;
-    const int tiles = (prefix_len + PF_KT - 1) / PF_KT;
-    pa.keys_per_split = ((tiles + nsp - 1) / nsp) * PF_KT;
-    pa.scale_log2 = br.scale_log2;
-    const int rep = H / Hkv, rows = B * rep;
-    const size_t smem = 4 * PF_TILE_BYTES;  // two stages of K and V (also covers 128 staged Q rows)
-    if (rows <= 64) {
-      cudaError_t e = cudaFuncSetAttribute(attn_prefix_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
-      attn_prefix_kernel<4><<<dim3(nsp, Hkv, 1), 128, smem, st>>>(pa);
-    } else {
-      cudaError_t e = cudaFuncSetAttribute(attn_prefix_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
-      attn_prefix_kernel<8><<<dim3(nsp, Hkv, (rows + 127) / 128), 256, smem, st>>>(pa);
-    }
-    Q40_LAUNCH_CHECK();
+    int rc = launch_prefix(pa, nsp, st);
+    if (rc != Q40_OK) return rc;
     br.pm = pm; br.pl = pl; br.po = po; br.nsp = nsp;
   }
   // Lmax == 0: the branch kernel only merges the prefix partials
   const int mode = (Lmax == 0) ? 0 : (idx_bytes == 2 ? 1 : 2);
   if (Lmax == 0) { br.seq_lens = nullptr; br.L = 0; }
   return launch_branch(br, mode, B, st);
+}
+
+extern "C" int q40_attn_tree_decode(const void* q, const void* prefix_k, const void* prefix_v,
+                                    int max_prefix_len, const int32_t* prefix_len_dev,
+                                    int64_t prefix_key_stride, int64_t prefix_head_stride,
+                                    const void* cache_kq, const void* cache_ks, const void* cache_vq,
+                                    const void* cache_vs, int max_t, const int32_t* pos_dev,
+                                    const void* cur_k, const void* cur_v, int64_t cur_stride, void* o, int B,
+                                    int H, int Hkv, int D, void* workspace, size_t workspace_bytes,
+                                    void* stream) {
+  using namespace q40;
+  if (!q || !o || !prefix_k || !prefix_v || !prefix_len_dev || !pos_dev) return Q40_E_NULL;
+  if (!cache_kq || !cache_ks || !cache_vq || !cache_vs) return Q40_E_NULL;
+  if ((cur_k == nullptr) != (cur_v == nullptr)) return Q40_E_NULL;
+  if (D != ATTN_D) return Q40_E_UNSUPPORTED;
+  if (B < 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0 || max_prefix_len <= 0 || max_t <= 0) return Q40_E_SHAPE;
+  if (prefix_key_stride % 8 != 0 || prefix_head_stride % 8 != 0 || cur_stride % 8 != 0) return Q40_E_ALIGN;
+  if (B == 0) return Q40_OK;
+  if (!q40_aligned(q, 16) || !q40_aligned(prefix_k, 16) || !q40_aligned(prefix_v, 16) ||
+      !q40_aligned(cache_kq, 16) || !q40_aligned(cache_vq, 16) || !q40_aligned(cur_k, 16) ||
+      !q40_aligned(cur_v, 16))
+    return Q40_E_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t rows_total = (int64_t)B * H;
+  const int nsp = prefix_splits(B, H, Hkv, max_prefix_len);
+  const size_t need = (size_t)nsp * rows_total * (D + 2) * sizeof(float);
+  if (!workspace || workspace_bytes < need) return Q40_E_WORKSPACE;
+  if (!q40_aligned(workspace, 16)) return Q40_E_ALIGN;
+  float* po = (float*)workspace;
+  float* pm = po + (size_t)nsp * rows_total * D;
+  float* pl = pm + (size_t)nsp * rows_total;
+  PrefixArgs pa{};
+  pa.q = (const __half*)q; pa.pk = (const __half*)prefix_k; pa.pv = (const __half*)prefix_v;
+  pa.pm = pm; pa.pl = pl; pa.po = po;
+  pa.key_stride = prefix_key_stride; pa.head_stride = prefix_head_stride;
+  pa.prefix_len_dev = prefix_len_dev;
+  pa.B = B; pa.H = H; pa.Hkv = Hkv; pa.prefix_len = max_prefix_len;
+  pa.scale_log2 = attn_scale_log2(D);
+  int rc = launch_prefix(pa, nsp, st);
+  if (rc != Q40_OK) return rc;
+  BranchArgs br{};
+  br.q = (const __half*)q; br.o = (__half*)o;
+  br.H = H; br.Hkv = Hkv; br.L = max_t;
+  br.scale_log2 = pa.scale_log2;
+  br.pm = pm; br.pl = pl; br.po = po; br.nsp = nsp;
+  br.kq = (const int8_t*)cache_kq; br.ksc = (const __half*)cache_ks;
+  br.vq = (const int8_t*)cache_vq; br.vsc = (const __half*)cache_vs;
+  br.pos = pos_dev; br.prefix_len = prefix_len_dev; br.max_t = max_t;
+  br.cur_k = (const __half*)cur_k; br.cur_v = (const __half*)cur_v; br.cur_stride = cur_stride;
+  return launch_branch(br, 3, B, st);
 }

@@ -1,0 +1,412 @@
+"""Llama-architecture decoder with Q4_0 linears, a shared fp16 prompt KV cache and a Q4_0
+per-branch suffix cache: the host-side mirror of the reference's
+hf_model_q40_kv_shared.Transformer (same class and attribute names, same
+forward(tokens, start_pos) / fork / resetSeq calls, same checkpoint tensors
+`.w`/`.s`/`.shape` per linear), running on the q40b200 kernels.
+
+What differs from the reference is how a decode step executes, not what it computes:
+  * the whole step is one CUDA graph per batch width (positions and lengths live in device
+    memory, so the graph is replayed for every token);
+  * attention reads the shared prompt cache once for all branches and the packed Q4_0
+    suffix rows directly, instead of dequantising the whole suffix, concatenating it with a
+    per-branch expansion of the prompt and calling SDPA (hf_model_q40_kv_shared.py:346-405);
+  * the rounding points of the reference are kept: RMSNorm (fp32 inside, fp16 out, fp16
+    weight), fp16(code*scale) weights with fp32 accumulation, fp16 rotary embedding, the
+    token being decoded attends to its own un-quantised K/V while later steps see its Q4_0
+    round trip, fp16 residual adds, fp16 SiLU-mul.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from . import kernels as K
+from ._lib import check, lib
+
+DTYPE = torch.float16
+GROUP_SIZE = 64
+
+
+@dataclass
+class ModelArgs:
+    """Same fields and defaults as the reference's ModelArgs (hf_model_q40_kv_shared.py:58-72)."""
+    dim: int = 4096
+    n_layers: int = 32
+    n_heads: int = 32
+    n_kv_heads: Optional[int] = None
+    vocab_size: int = 32016
+    multiple_of: int = 256
+    ffn_dim_multiplier: Optional[float] = None
+    norm_eps: float = 1e-5
+    rope_theta: float = 1000000.0
+
+    max_batch_size: int = 80
+    max_seq_len: int = 256
+    max_prompt_seq_len: int = 256
+
+
+def precompute_freqs_cis(dim: int, end: int, theta: float = 10000.0):
+    """fp32 angles exactly as the reference (hf_model_q40_kv_shared.py:137-142)."""
+    freqs = 1.0 / (theta ** (torch.arange(0, dim, 2)[: (dim // 2)].float() / dim))
+    t = torch.arange(end, device=freqs.device, dtype=torch.float32)
+    freqs = torch.outer(t, freqs)
+    return torch.polar(torch.ones_like(freqs), freqs)
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim: int, eps: float = 1e-6):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(dim), requires_grad=False)
+
+    def forward(self, x):
+        return K.rmsnorm(x, self.weight.to(DTYPE), self.eps)
+
+
+class LinearQ4_0(nn.Module):
+    """Holder of one packed weight, as in the reference (hf_model_q40_kv_shared.py:217-236):
+    `w` int8 [in*out/128, 64], `s` fp16 [in*out/64], `shape` = (in_features, out_features)
+    until a loader overwrites it with the checkpoint's (out, in) — either way the call below
+    passes (shape[1], shape[0]) like the reference does."""
+
+    def __init__(self, in_features, out_features, group_size):
+        super().__init__()
+        self.group_size = group_size
+        # placeholders; a loader assigns the checkpoint tensors (already on the device)
+        self.w = torch.empty((in_features * out_features // group_size // 2, group_size), dtype=torch.int8,
+                             device="meta")
+        self.s = torch.empty(in_features * out_features // group_size, dtype=DTYPE, device="meta")
+        self.shape = (in_features, out_features)
+
+    def kn(self):
+        """(K, N) of the stored [K, N] matrix."""
+        return int(self.shape[1]), int(self.shape[0])
+
+    def forward(self, x):
+        shape = x.shape
+        x2 = x.reshape(shape[0] * shape[1], -1)
+        y = K.matmul_q40(x2.contiguous(), self.w, self.s, self.kn(), group_size=self.group_size)
+        return y.view(shape[0], shape[1], -1)
+
+
+class Attention(nn.Module):
+    def __init__(self, args: ModelArgs, layer_id: int, caches):
+        super().__init__()
+        self.args = args
+        self.n_kv_heads = args.n_heads if args.n_kv_heads is None else args.n_kv_heads
+        assert args.n_heads % self.n_kv_heads == 0
+        self.n_local_heads = args.n_heads
+        self.n_local_kv_heads = self.n_kv_heads
+        self.n_rep = self.n_local_heads // self.n_local_kv_heads
+        self.head_dim = args.dim // args.n_heads
+        self.wq = LinearQ4_0(args.dim, args.n_heads * self.head_dim, GROUP_SIZE)
+        self.wk = LinearQ4_0(args.dim, self.n_kv_heads * self.head_dim, GROUP_SIZE)
+        self.wv = LinearQ4_0(args.dim, self.n_kv_heads * self.head_dim, GROUP_SIZE)
+        self.wo = LinearQ4_0(args.n_heads * self.head_dim, args.dim, GROUP_SIZE)
+        # views into the model-wide cache tensors (same names as the reference's attributes)
+        self.cache_prompt_k = caches["pk"][layer_id]     # [maxP, Hkv, D] fp16
+        self.cache_prompt_v = caches["pv"][layer_id]
+        self.cache_k = caches["kq"][layer_id]            # [maxB, maxT, Hkv, 64] int8
+        self.cache_k_s = caches["ks"][layer_id]          # [maxB, maxT, Hkv, 2] fp16
+        self.cache_v = caches["vq"][layer_id]
+        self.cache_v_s = caches["vs"][layer_id]
+        self.cache_prompt_len = 0
+
+
+class FeedForward(nn.Module):
+    def __init__(self, dim: int, hidden_dim: int, multiple_of: int, ffn_dim_multiplier: Optional[float]):
+        super().__init__()
+        hidden_dim = int(2 * hidden_dim / 3)
+        if ffn_dim_multiplier is not None:
+            hidden_dim = int(ffn_dim_multiplier * hidden_dim)
+        hidden_dim = multiple_of * ((hidden_dim + multiple_of - 1) // multiple_of)
+        self.hidden_dim = hidden_dim
+        self.w1 = LinearQ4_0(dim, hidden_dim, GROUP_SIZE)
+        self.w2 = LinearQ4_0(hidden_dim, dim, GROUP_SIZE)
+        self.w3 = LinearQ4_0(dim, hidden_dim, GROUP_SIZE)
+
+    def forward(self, x):
+        return self.w2(K.silu_mul(self.w1(x), self.w3(x)))
+
+
+class TransformerBlock(nn.Module):
+    def __init__(self, layer_id: int, args: ModelArgs, caches):
+        super().__init__()
+        self.n_heads = args.n_heads
+        self.dim = args.dim
+        self.head_dim = args.dim // args.n_heads
+        self.attention = Attention(args, layer_id, caches)
+        self.feed_forward = FeedForward(dim=args.dim, hidden_dim=4 * args.dim, multiple_of=args.multiple_of,
+                                        ffn_dim_multiplier=args.ffn_dim_multiplier)
+        self.layer_id = layer_id
+        self.attention_norm = RMSNorm(args.dim, eps=args.norm_eps)
+        self.ffn_norm = RMSNorm(args.dim, eps=args.norm_eps)
+
+
+class Transformer(nn.Module):
+    """forward(tokens, start_pos): start_pos == 0 is the prompt (batch 1; fills the shared
+    prompt cache), start_pos > 0 with one token per branch is a decode step
+    (hf_model_q40_kv_shared.py:492-510)."""
+
+    def __init__(self, params: ModelArgs, device: Optional[torch.device] = None):
+        super().__init__()
+        if not torch.cuda.is_available():
+            raise RuntimeError("spec_mcts_b200.model needs a CUDA device (no CPU path)")
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.params = params
+        self.vocab_size = params.vocab_size
+        self.n_layers = params.n_layers
+        p = params
+        Hkv = p.n_heads if p.n_kv_heads is None else p.n_kv_heads
+        D = p.dim // p.n_heads
+        assert D == 128, "the attention kernels are written for head_dim 128"
+        L, dev = p.n_layers, self.device
+        self._caches = {
+            "pk": torch.zeros((L, p.max_prompt_seq_len, Hkv, D), dtype=DTYPE, device=dev),
+            "pv": torch.zeros((L, p.max_prompt_seq_len, Hkv, D), dtype=DTYPE, device=dev),
+            "kq": torch.zeros((L, p.max_batch_size, p.max_seq_len, Hkv, 64), dtype=torch.int8, device=dev),
+            "ks": torch.zeros((L, p.max_batch_size, p.max_seq_len, Hkv, 2), dtype=DTYPE, device=dev),
+            "vq": torch.zeros((L, p.max_batch_size, p.max_seq_len, Hkv, 64), dtype=torch.int8, device=dev),
+            "vs": torch.zeros((L, p.max_batch_size, p.max_seq_len, Hkv, 2), dtype=DTYPE, device=dev),
+        }
+        self.tok_embeddings = nn.Embedding(p.vocab_size, p.dim, device="meta")
+        self.layers = nn.ModuleList(TransformerBlock(i, p, self._caches) for i in range(p.n_layers))
+        self.norm = RMSNorm(p.dim, eps=p.norm_eps)
+        self.output = nn.Linear(p.dim, p.vocab_size, bias=False, device="meta")
+        self.freqs_cis = precompute_freqs_cis(D, p.max_seq_len + p.max_prompt_seq_len, p.rope_theta)
+        self._n_pos = p.max_seq_len + p.max_prompt_seq_len
+        self._cos = self.freqs_cis.real.to(DTYPE).contiguous().to(dev)   # [n_pos, 64]
+        self._sin = self.freqs_cis.imag.to(DTYPE).contiguous().to(dev)
+        self._Hkv, self._D = Hkv, D
+        self._prefix_len_dev = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._pos_dev = torch.zeros(p.max_batch_size, dtype=torch.int32, device=dev)
+        self._tok_dev = torch.zeros(p.max_batch_size, dtype=torch.int64, device=dev)
+        self._graphs = {}
+        self._bufs = {}
+        self.use_cuda_graph = True
+        # when set, a decode step also writes argmax(logits) back as the next input token and
+        # advances the positions on the device, so steps can be replayed without the host
+        self.greedy_feedback = False
+        # kernels of this library enqueued by one decode step (per layer: 2 norms, 7 matmuls,
+        # rope+append, 2 attention, SiLU-mul; plus the final norm)
+        self.launches_per_step = params.n_layers * 13 + 1
+
+    # ------------------------------------------------------------------ reference API
+    @torch.inference_mode()
+    def forward(self, tokens: torch.Tensor, start_pos: int):
+        bsz, seqlen = tokens.shape
+        if start_pos == 0:
+            return self._prefill(tokens)
+        assert seqlen == 1, "decode steps take one token per branch"
+        return self._decode(tokens, start_pos)
+
+    def fork(self, origin: int, curr_batch: int, forks: int):
+        """Copy branch `origin`'s suffix cache to `forks` new branches starting at index
+        curr_batch, in every layer (hf_model_q40_kv_shared.py:282-297, 512-516)."""
+        if forks <= 0:
+            return
+        for name in ("kq", "ks", "vq", "vs"):
+            c = self._caches[name]
+            c[:, curr_batch:curr_batch + forks] = c[:, origin:origin + 1]
+
+    def resetSeq(self):
+        for layer in self.layers:
+            layer.attention.cache_prompt_len = 0
+        self._prefix_len_dev.zero_()
+
+    # ------------------------------------------------------------------ prompt
+    def _prefill(self, tokens):
+        p = self.params
+        bsz, S = tokens.shape
+        assert bsz == 1, "the prompt is processed once and shared by all branches"
+        assert S <= p.max_prompt_seq_len
+        dev = self.device
+        H, Hkv, D = p.n_heads, self._Hkv, self._D
+        h = self.tok_embeddings(tokens.to(dev)).to(DTYPE).view(S, p.dim)
+        pos = torch.arange(S, dtype=torch.int32, device=dev)
+        for li, layer in enumerate(self.layers):
+            att, ff = layer.attention, layer.feed_forward
+            xn = K.rmsnorm(h, layer.attention_norm.weight, p.norm_eps)
+            xq = K.matmul_q40(xn, att.wq.w, att.wq.s, att.wq.kn()).view(S, H, D)
+            xk = K.matmul_q40(xn, att.wk.w, att.wk.s, att.wk.kn()).view(S, Hkv, D)
+            xv = K.matmul_q40(xn, att.wv.w, att.wv.s, att.wv.kn()).view(S, Hkv, D)
+            K.rope_(xq, pos, self._cos, self._sin)
+            K.rope_(xk, pos, self._cos, self._sin)
+            att.cache_prompt_k[:S] = xk
+            att.cache_prompt_v[:S] = xv
+            att.cache_prompt_len = S
+            # causal attention over the prompt: dense batched attention is library territory
+            q_ = xq.transpose(0, 1).unsqueeze(0)
+            k_ = xk.transpose(0, 1).unsqueeze(0)
+            v_ = xv.transpose(0, 1).unsqueeze(0)
+            if Hkv != H:
+                k_ = k_.repeat_interleave(H // Hkv, dim=1)
+                v_ = v_.repeat_interleave(H // Hkv, dim=1)
+            o = F.scaled_dot_product_attention(q_, k_, v_, is_causal=True)
+            o = o[0].transpose(0, 1).reshape(S, H * D)
+            ao = K.matmul_q40(o.contiguous(), att.wo.w, att.wo.s, att.wo.kn())
+            hn, h = K.rmsnorm(h, layer.ffn_norm.weight, p.norm_eps, residual=ao)
+            a1 = K.matmul_q40(hn, ff.w1.w, ff.w1.s, ff.w1.kn())
+            a3 = K.matmul_q40(hn, ff.w3.w, ff.w3.s, ff.w3.kn())
+            f2 = K.matmul_q40(K.silu_mul(a1, a3), ff.w2.w, ff.w2.s, ff.w2.kn())
+            h = h + f2
+        self._prefix_len_dev.fill_(S)
+        hn = K.rmsnorm(h, self.norm.weight, p.norm_eps)
+        return F.linear(hn, self.output.weight).to(DTYPE).view(1, S, -1)
+
+    # ------------------------------------------------------------------ decode
+    def _buffers(self, B):
+        b = self._bufs.get(B)
+        if b is None:
+            p, dev = self.params, self.device
+            H, Hkv, D = p.n_heads, self._Hkv, self._D
+            hid = self.layers[0].feed_forward.hidden_dim
+            e = lambda *s: torch.empty(s, dtype=DTYPE, device=dev)
+            nb_attn = lib.q40_attn_shared_prefix_workspace_bytes(B, H, D, p.max_prompt_seq_len)
+            nb_gemm = max(lib.q40_gemm_workspace_bytes(B, n, k) for (n, k) in
+                          [(H * D, p.dim), (hid, p.dim), (p.dim, hid), (p.dim, H * D)])
+            b = dict(h=e(B, p.dim), xn=e(B, p.dim), q=e(B, H * D), k=e(B, Hkv * D), v=e(B, Hkv * D),
+                     ao=e(B, H * D), o=e(B, p.dim), a1=e(B, hid), a3=e(B, hid), g=e(B, hid), f=e(B, p.dim),
+                     attn_ws=torch.empty(nb_attn, dtype=torch.uint8, device=dev),
+                     gemm_ws=torch.zeros(nb_gemm, dtype=torch.uint8, device=dev),
+                     logits=e(B, p.vocab_size))
+            self._bufs[B] = b
+        return b
+
+    def _gemm(self, bufs, x, lin: LinearQ4_0, out, st):
+        Kd, N = lin.kn()
+        ws = bufs["gemm_ws"]
+        check(lib.q40_gemm_kn(x.data_ptr(), x.stride(0), lin.w.data_ptr(), lin.s.data_ptr(), out.data_ptr(),
+                              out.stride(0), x.shape[0], N, Kd, lin.group_size, ws.data_ptr(), ws.numel(), st),
+              "q40_gemm_kn")
+
+    def _decode_body(self, B):
+        """Enqueue one decode step for B branches on the current stream (captured into a graph)."""
+        p, bufs = self.params, self._buffers(B)
+        H, Hkv, D = p.n_heads, self._Hkv, self._D
+        self._check_loaded()
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        h, xn = bufs["h"], bufs["xn"]
+        h.copy_(self.tok_embeddings(self._tok_dev[:B]).to(DTYPE))
+        pos, plen = self._pos_dev, self._prefix_len_dev
+        aws = bufs["attn_ws"]
+        pending = None     # output of the previous sub-block, added to h by the next norm kernel
+        for layer in self.layers:
+            att, ff = layer.attention, layer.feed_forward
+            self._norm(h, pending, layer.attention_norm.weight, xn, st)
+            self._gemm(bufs, xn, att.wq, bufs["q"], st)
+            self._gemm(bufs, xn, att.wk, bufs["k"], st)
+            self._gemm(bufs, xn, att.wv, bufs["v"], st)
+            check(lib.q40_rope_kv_append(bufs["q"].data_ptr(), H * D, bufs["k"].data_ptr(), Hkv * D,
+                                         bufs["v"].data_ptr(), Hkv * D, pos.data_ptr(), plen.data_ptr(),
+                                         self._cos.data_ptr(), self._sin.data_ptr(), self._n_pos,
+                                         att.cache_k.data_ptr(), att.cache_k_s.data_ptr(),
+                                         att.cache_v.data_ptr(), att.cache_v_s.data_ptr(), B, H, Hkv, D,
+                                         p.max_seq_len, st), "q40_rope_kv_append")
+            pk, pv = att.cache_prompt_k, att.cache_prompt_v
+            check(lib.q40_attn_tree_decode(bufs["q"].data_ptr(), pk.data_ptr(), pv.data_ptr(),
+                                           p.max_prompt_seq_len, plen.data_ptr(), pk.stride(0), pk.stride(1),
+                                           att.cache_k.data_ptr(), att.cache_k_s.data_ptr(),
+                                           att.cache_v.data_ptr(), att.cache_v_s.data_ptr(), p.max_seq_len,
+                                           pos.data_ptr(), bufs["k"].data_ptr(), bufs["v"].data_ptr(), Hkv * D,
+                                           bufs["ao"].data_ptr(), B, H, Hkv, D, aws.data_ptr(), aws.numel(), st),
+                  "q40_attn_tree_decode")
+            self._gemm(bufs, bufs["ao"], att.wo, bufs["o"], st)
+            self._norm(h, bufs["o"], layer.ffn_norm.weight, xn, st)
+            self._gemm(bufs, xn, ff.w1, bufs["a1"], st)
+            self._gemm(bufs, xn, ff.w3, bufs["a3"], st)
+            check(lib.q40_silu_mul(bufs["a1"].data_ptr(), bufs["a3"].data_ptr(), bufs["g"].data_ptr(),
+                                   bufs["g"].numel(), st), "q40_silu_mul")
+            self._gemm(bufs, bufs["g"], ff.w2, bufs["f"], st)
+            pending = bufs["f"]
+        self._norm(h, pending, self.norm.weight, xn, st)
+        torch.matmul(xn, self.output.weight.t(), out=bufs["logits"])
+        if self.greedy_feedback:
+            self._tok_dev[:B].copy_(bufs["logits"].argmax(dim=-1))
+            self._pos_dev[:B] += 1
+        return bufs["logits"]
+
+    def _check_loaded(self):
+        for t in (self.norm.weight, self.layers[0].attention_norm.weight, self.output.weight,
+                  self.tok_embeddings.weight, self.layers[0].attention.wq.w):
+            if not t.is_cuda or (t.is_floating_point() and t.dtype != DTYPE):
+                raise RuntimeError("model weights must be loaded and moved with model.to(device, float16) "
+                                   "before the first step (found a %s %s tensor)" % (t.device, t.dtype))
+
+    def _norm(self, h, residual, weight, out, st):
+        """out = RMSNorm(h + residual) with h updated in place (residual may be None)."""
+        p = self.params
+        check(lib.q40_rmsnorm(h.data_ptr(), residual.data_ptr() if residual is not None else None,
+                              weight.data_ptr(), out.data_ptr(), h.data_ptr() if residual is not None else None,
+                              h.shape[0], p.dim, float(p.norm_eps), st), "q40_rmsnorm")
+
+    def _decode(self, tokens, start_pos):
+        B = tokens.shape[0]
+        assert B <= self.params.max_batch_size
+        self._tok_dev[:B].copy_(tokens.reshape(B), non_blocking=True)
+        self._pos_dev[:B].fill_(start_pos)
+        logits = self.decode_replay(B)
+        return logits.view(B, 1, -1)
+
+    def decode_replay(self, B):
+        """Run one decode step for B branches with the tokens/positions already in the device
+        buffers (`_tok_dev`, `_pos_dev`); returns the static logits buffer [B, vocab]."""
+        if not self.use_cuda_graph:
+            return self._decode_body(B)
+        key = (B, self.greedy_feedback)
+        g = self._graphs.get(key)
+        if g is None:
+            # torch requires capture on a side stream after a warm-up run
+            s = torch.cuda.Stream(self.device)
+            s.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(s):
+                self._decode_body(B)
+            torch.cuda.current_stream(self.device).wait_stream(s)
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._decode_body(B)
+            self._graphs[key] = g
+            if self.greedy_feedback:
+                # the warm-up run advanced the device-side position and token once: undo that
+                # (capture itself executes nothing)
+                self._pos_dev[:B] -= 1
+        g.replay()
+        return self._bufs[B]["logits"]
+
+
+def random_init_(model: Transformer, seed: int = 0, std: float = 0.02) -> None:
+    """Fill a model with N(0, std^2) weights quantised on the device by the library's own
+    packer (norm weights = 1): the synthetic stand-in for a CodeLlama checkpoint converted
+    by the reference's fp16_to_int4.py (which stores quantize_q40(W.t()) per linear)."""
+    dev = model.device
+    g = torch.Generator(device=dev).manual_seed(seed)
+    p = model.params
+
+    def fill(lin: LinearQ4_0, in_f, out_f):
+        wt = (torch.randn((in_f, out_f), generator=g, device=dev, dtype=torch.float32) * std).to(DTYPE)
+        q, s = K.quantize_q40(wt, GROUP_SIZE)       # [K, N] row-major: groups along N
+        lin.w, lin.s, lin.shape = q, s.view(-1), (out_f, in_f)
+
+    for layer in model.layers:
+        att, ff = layer.attention, layer.feed_forward
+        H, Hkv, D = p.n_heads, model._Hkv, model._D
+        fill(att.wq, p.dim, H * D)
+        fill(att.wk, p.dim, Hkv * D)
+        fill(att.wv, p.dim, Hkv * D)
+        fill(att.wo, H * D, p.dim)
+        fill(ff.w1, p.dim, ff.hidden_dim)
+        fill(ff.w3, p.dim, ff.hidden_dim)
+        fill(ff.w2, ff.hidden_dim, p.dim)
+        for n in (layer.attention_norm, layer.ffn_norm):
+            n.weight = nn.Parameter(torch.ones(p.dim, dtype=DTYPE, device=dev), requires_grad=False)
+    model.norm.weight = nn.Parameter(torch.ones(p.dim, dtype=DTYPE, device=dev), requires_grad=False)
+    emb = (torch.randn((p.vocab_size, p.dim), generator=g, device=dev) * std).to(DTYPE)
+    out = (torch.randn((p.vocab_size, p.dim), generator=g, device=dev) * std).to(DTYPE)
+    model.tok_embeddings = nn.Embedding.from_pretrained(emb, freeze=True)
+    model.output = nn.Linear(p.dim, p.vocab_size, bias=False, device=dev, dtype=DTYPE)
+    model.output.weight = nn.Parameter(out, requires_grad=False)

@@ -1,0 +1,91 @@
+"""Model-level parity on the GPU: the q40b200 model class against logits and greedy tokens
+produced by the reference's own model class (run on CPU by tests/golden/make_golden_model.py)
+for prefill -> fork -> 12 decode steps on 3 branches of a small geometry."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def small():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return np.load(os.path.join(ROOT, "tests", "golden", "model_small.npz"))
+
+
+def build_model(g, use_graph):
+    """Load exactly the way the reference's load_q40.py does: state dict for embedding / norms /
+    lm_head, then per-linear assignment of .w / .s / .shape, then model.to(device, fp16)."""
+    from spec_mcts_b200.model import ModelArgs, Transformer
+    args = ModelArgs(dim=256, n_layers=2, n_heads=2, vocab_size=512, multiple_of=128,
+                     max_batch_size=4, max_seq_len=16, max_prompt_seq_len=32)
+    model = Transformer(args)
+    sd = {k[3:]: torch.from_numpy(g[k]) for k in g.files if k.startswith("sd.")}
+    model.load_state_dict(sd, strict=False, assign=True)
+    for i, layer in enumerate(model.layers):
+        for name in ("attention.wq", "attention.wk", "attention.wv", "attention.wo",
+                     "feed_forward.w1", "feed_forward.w2", "feed_forward.w3"):
+            mod = layer
+            for part in name.split("."):
+                mod = getattr(mod, part)
+            mod.w = torch.from_numpy(g[f"q.layers.{i}.{name}.w"]).to("cuda")
+            mod.s = torch.from_numpy(g[f"q.layers.{i}.{name}.s"]).to("cuda")
+            mod.shape = tuple(int(v) for v in g[f"q.layers.{i}.{name}.shape"])
+    model = model.to("cuda", torch.float16)
+    model.use_cuda_graph = use_graph
+    return model
+
+
+def logits_close(a, b):
+    np.testing.assert_allclose(a.astype(np.float32), b.astype(np.float32), rtol=2e-2, atol=0.15)
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_small_model_matches_reference_class(small, use_graph):
+    g = small
+    model = build_model(g, use_graph)
+    prompt = torch.from_numpy(g["prompt"]).cuda()
+    logits = model(prompt, 0)
+    assert logits.shape == (1, prompt.shape[1], 512)
+    logits_close(logits[0, -1].cpu().numpy(), g["prefill_logits_last"])
+    B = 3
+    model.fork(0, 1, B - 1)
+    toks = torch.from_numpy(g["first_tokens"]).cuda()
+    pos = prompt.shape[1]
+    ref_logits, ref_toks = g["decode_logits"], g["decode_tokens"]
+    srt = np.sort(ref_logits.astype(np.float32), axis=-1)
+    margin = srt[..., -1] - srt[..., -2]
+    for step in range(ref_logits.shape[0]):
+        lg = model(toks, pos)[:, -1]
+        got = lg.float().cpu().numpy()
+        logits_close(got, ref_logits[step])
+        am = got.argmax(-1)
+        for b in range(B):
+            if margin[step, b] > 0.2:
+                assert am[b] == ref_toks[step, b], (step, b, margin[step, b])
+        # teacher forcing: continue from the reference's tokens so that a near-tie cannot
+        # make the sequences diverge
+        toks = torch.from_numpy(ref_toks[step]).view(B, 1).cuda()
+        pos += 1
+
+
+def test_fork_copies_suffix_cache(small):
+    model = build_model(small, False)
+    prompt = torch.from_numpy(small["prompt"]).cuda()
+    model(prompt, 0)
+    t = torch.tensor([[5]], device="cuda")
+    model(t, prompt.shape[1])
+    model.fork(0, 1, 2)
+    att = model.layers[1].attention
+    assert torch.equal(att.cache_k[1], att.cache_k[0]) and torch.equal(att.cache_v_s[2], att.cache_v_s[0])
+    assert int(att.cache_k[0].abs().sum()) > 0 and int(att.cache_k[3].abs().sum()) == 0
+    # identical branches produce identical logits
+    lg = model(torch.tensor([[7], [7], [7]], device="cuda"), prompt.shape[1] + 1)
+    assert torch.equal(lg[0], lg[1]) and torch.equal(lg[0], lg[2])
+    model.resetSeq()
+    assert int(model._prefix_len_dev.item()) == 0

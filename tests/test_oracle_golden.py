@@ -113,3 +113,21 @@ def test_silu_mul(golden):
     ref = golden["ep.silu.y"]
     d = np.abs(y.view(np.int16).astype(np.int32) - ref.view(np.int16).astype(np.int32))
     assert d.max() <= 1 and (d > 0).mean() < 0.01
+
+
+def test_cpu_path_matches_golden(golden):
+    """The torch CPU restatement that bench.py times is the same arithmetic as the reference's."""
+    import torch
+    from oracle import cpu_path as C
+    w = torch.from_numpy(golden["q.w_normal.w"])
+    q, s = C.quantize(w, 64)
+    np.testing.assert_array_equal(q.numpy(), golden["q.w_normal.g64.packed"])
+    np.testing.assert_array_equal(s.numpy().view(np.uint16), golden["q.w_normal.g64.scale"].view(np.uint16))
+    d = C.dequantize(q, s, 64, tuple(w.shape))
+    np.testing.assert_array_equal(d.numpy().view(np.uint16), golden["q.w_normal.g64.deq"].view(np.uint16))
+    y, _, _ = C.linear_kn(torch.from_numpy(golden["mm.kn.m3.a"]), torch.from_numpy(golden["mm.kn.bw"]),
+                          torch.from_numpy(golden["mm.kn.bs"]), (256, 384))
+    np.testing.assert_array_equal(y.numpy().view(np.uint16), golden["mm.kn.m3.c"].view(np.uint16))
+    y, _, _ = C.linear_nk(torch.from_numpy(golden["mm.nk.x"]), torch.from_numpy(golden["mm.nk.wq"]),
+                          torch.from_numpy(golden["mm.nk.ws"]), (384, 256))
+    np.testing.assert_array_equal(y.numpy().view(np.uint16), golden["mm.nk.y"].view(np.uint16))
