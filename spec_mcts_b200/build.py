@@ -35,14 +35,26 @@ def sources():
     return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
 
 
-def _deps_mtime() -> float:
-    files = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + \
-        glob.glob(os.path.join(PKG_DIR, "..", "include", "*.h")) + [os.path.abspath(__file__)]
-    return max(os.path.getmtime(f) for f in files)
+STAMP = LIB + ".sha"
+
+
+def _sources_digest() -> str:
+    """Content hash of everything the library is built from (file times do not survive a
+    copy of the tree to another machine, contents do)."""
+    import hashlib
+    files = sources() + sorted(glob.glob(os.path.join(CSRC, "*.cuh"))) + \
+        sorted(glob.glob(os.path.join(PKG_DIR, "..", "include", "*.h")))
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    for f in files:
+        h.update(os.path.basename(f).encode())
+        h.update(open(f, "rb").read())
+    return h.hexdigest()
 
 
 def needs_build() -> bool:
-    return not os.path.exists(LIB) or os.path.getmtime(LIB) < _deps_mtime()
+    if not os.path.exists(LIB) or not os.path.exists(STAMP):
+        return True
+    return open(STAMP).read().strip() != _sources_digest()
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
@@ -72,6 +84,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    with open(STAMP, "w") as f:
+        f.write(_sources_digest())
     return LIB
 
 

@@ -334,6 +334,7 @@ extern "C" int q40_attn_shared_prefix(const void* q, const void* prefix_k, const
     pa.pm = pm; pa.pl = pl; pa.po = po;
     pa.key_stride = prefix_key_stride; pa.head_stride = prefix_head_stride;
     pa.B = B; pa.H = H; pa.Hkv = Hkv; pa.prefix_len = prefix_len;
+    pa.scale_log2 = br.scale_log2;
     int rc = launch_prefix(pa, nsp, st);
     if (rc != Q40_OK) return rc;
     br.pm = pm; br.pl = pl; br.po = po; br.nsp = nsp;
