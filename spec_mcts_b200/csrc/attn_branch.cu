@@ -50,6 +50,9 @@ attn_branch_kernel(const BranchArgs a) {
   const int hk = h / (a.H / a.Hkv);
   const int tid = threadIdx.x, lane = tid & 31;
   const int grp = tid >> 3, sub = tid & 7;
+  // the 8 lanes that share a key; groups of one warp may run different numbers of iterations,
+  // so every shuffle names only its own group
+  const unsigned gmask = 0xffu << (lane & 24);
   int len;
   if (MODE == 3) len = min(max(a.pos[b] - a.prefix_len[0], 0), a.max_t);
   else len = a.seq_lens ? min(max(a.seq_lens[b], 0), a.L) : a.L;
@@ -106,9 +109,9 @@ attn_branch_kernel(const BranchArgs a) {
         acc = fmaf(qf[2 * i], f.x, acc);
         acc = fmaf(qf[2 * i + 1], f.y, acc);
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      acc += __shfl_xor_sync(gmask, acc, 1);
+      acc += __shfl_xor_sync(gmask, acc, 2);
+      acc += __shfl_xor_sync(gmask, acc, 4);
       s[u] = (t0 + u * BR_GROUPS < len) ? acc : -CUDART_INF_F;
       mnew = fmaxf(mnew, s[u]);
     }
@@ -170,9 +173,9 @@ attn_branch_kernel(const BranchArgs a) {
           acc = fmaf(qf[4 * wi + 1], f13.x, acc);
           acc = fmaf(qf[4 * wi + 3], f13.y, acc);
         }
-        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+        acc += __shfl_xor_sync(gmask, acc, 1);
+        acc += __shfl_xor_sync(gmask, acc, 2);
+        acc += __shfl_xor_sync(gmask, acc, 4);
         s[u] = (t0 + u * BR_GROUPS < len) ? acc : -CUDART_INF_F;
         mnew = fmaxf(mnew, s[u]);
       }
@@ -266,7 +269,6 @@ attn_branch_kernel(const BranchArgs a) {
   }
   const float outv = (Lsum > 0.f) ? acc / Lsum : 0.f;
   a.o[((int64_t)b * a.H + h) * D + d] = __float2half_rn(outv);
-  (void)lane;
 }
 
 int launch_branch(const BranchArgs& a, int mode, int B, cudaStream_t st) {

@@ -259,7 +259,7 @@ class Transformer(nn.Module):
         return F.linear(hn, self.output.weight).to(DTYPE).view(1, S, -1)
 
     # ------------------------------------------------------------------ decode
-    def _buffers(self, B):
+    def _step_buffers(self, B):
         b = self._bufs.get(B)
         if b is None:
             p, dev = self.params, self.device
@@ -286,7 +286,7 @@ class Transformer(nn.Module):
 
     def _decode_body(self, B):
         """Enqueue one decode step for B branches on the current stream (captured into a graph)."""
-        p, bufs = self.params, self._buffers(B)
+        p, bufs = self.params, self._step_buffers(B)
         H, Hkv, D = p.n_heads, self._Hkv, self._D
         self._check_loaded()
         st = torch.cuda.current_stream(self.device).cuda_stream
