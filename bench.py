@@ -272,6 +272,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--widths", default=",".join(str(w) for w in WIDTHS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--skip-prefill", action="store_true",
+                    help="profiling aid: fill the prompt cache with random K/V instead of running the prompt "
+                         "(keeps a profiler capture short); not a valid benchmark configuration")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -303,7 +306,12 @@ def main():
     g = torch.Generator().manual_seed(1)
     prompt = torch.randint(0, VOCAB, (1, PROMPT_LEN), generator=g)
     with torch.inference_mode():
-        model(prompt.to(dev), 0)
+        if args.skip_prefill:
+            model._caches["pk"].normal_()
+            model._caches["pv"].normal_()
+            model._prefix_len_dev.fill_(PROMPT_LEN)
+        else:
+            model(prompt.to(dev), 0)
         model.fork(0, 1, max(widths) - 1)
         torch.cuda.synchronize(dev)
 
@@ -350,6 +358,7 @@ def main():
             "config": {"workload": "codellama-7b-arch q4_0 decode (32 layers, hidden 4096, ffn 11008, vocab 32016), "
                                    "random-init N(0,0.02^2) weights, prompt 512 shared, greedy, width %d" % w0,
                        "group": 64, "prompt_len": PROMPT_LEN, "widths": widths, "replicas": world,
+                       "skip_prefill": bool(args.skip_prefill),
                        "l2": "inputs larger than L2 (3.7 GB of weights streamed per step)"},
             "by_width": {str(w): {"tokens_per_s": tok_s[w], "ms_per_step": results[w] / steps * 1e3,
                                   "e2e_tokens_per_s": e2e_tok_s[w]} for w in widths},

@@ -72,9 +72,10 @@ rope_kernel(__half* __restrict__ x, const int32_t* __restrict__ pos, const __hal
   const __half s = sin_tbl[(int64_t)p * half_d + d];
   __half* px = x + (int64_t)r * row_stride + (int64_t)h * D + d;
   const __half x1 = px[0], x2 = px[half_d];
-  // q*cos + rotate_half(q)*sin, every operation rounded to fp16
-  px[0] = __hadd(__hmul(x1, c), __hmul(__hneg(x2), s));
-  px[half_d] = __hadd(__hmul(x2, c), __hmul(x1, s));
+  // q*cos + rotate_half(q)*sin, every operation rounded to fp16 (the _rn forms are never
+  // contracted into a fused multiply-add)
+  px[0] = __hadd_rn(__hmul_rn(x1, c), __hmul_rn(__hneg(x2), s));
+  px[half_d] = __hadd_rn(__hmul_rn(x2, c), __hmul_rn(x1, s));
 }
 
 __global__ void __launch_bounds__(256)

@@ -57,15 +57,15 @@ rope_kv_append_kernel(const AppendArgs a) {
   if (hh < a.H) {   // a query head: rotate only
     __half* px = a.q + (int64_t)b * a.q_stride + hh * D + d;
     const __half x1 = px[0], x2 = px[HD];
-    px[0] = __hadd(__hmul(x1, c), __hmul(__hneg(x2), s));
-    px[HD] = __hadd(__hmul(x2, c), __hmul(x1, s));
+    px[0] = __hadd_rn(__hmul_rn(x1, c), __hmul_rn(__hneg(x2), s));
+    px[HD] = __hadd_rn(__hmul_rn(x2, c), __hmul_rn(x1, s));
     return;
   }
   const int hk = hh - a.H;
   __half* pk = a.k + (int64_t)b * a.k_stride + hk * D + d;
   const __half k1 = pk[0], k2 = pk[HD];
-  const __half r1 = __hadd(__hmul(k1, c), __hmul(__hneg(k2), s));
-  const __half r2 = __hadd(__hmul(k2, c), __hmul(k1, s));
+  const __half r1 = __hadd_rn(__hmul_rn(k1, c), __hmul_rn(__hneg(k2), s));
+  const __half r2 = __hadd_rn(__hmul_rn(k2, c), __hmul_rn(k1, s));
   pk[0] = r1;
   pk[HD] = r2;
   const __half* pv = a.v + (int64_t)b * a.v_stride + hk * D + d;
