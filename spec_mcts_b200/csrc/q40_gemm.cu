@@ -41,6 +41,22 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Sum of one element over the split-K partials, in split order (so the result does not depend
+// on which CTA arrives last) but with eight L2 loads in flight at a time.
+__device__ __forceinline__ float sum_partials(const float* __restrict__ p, int stride, int nsplit) {
+  float v = 0.f;
+  int sp = 0;
+  for (; sp + 8 <= nsplit; sp += 8) {
+    float t[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t[i] = __ldcg(p + (int64_t)(sp + i) * stride);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v += t[i];
+  }
+  for (; sp < nsplit; ++sp) v += __ldcg(p + (int64_t)sp * stride);
+  return v;
+}
+
 struct StepRegs {
   uint4 w[4];      // 16 packed bytes of rows 4t .. 4t+3
   uint32_t s[4];   // (scale of the high-nibble block, scale of the low-nibble block) per row
@@ -230,8 +246,7 @@ gemv_kn_kernel(const __half* __restrict__ A, int64_t lda, const uint8_t* __restr
   __threadfence();
   const float* base = part + ((int64_t)span * nsplit * M) * SPAN_COLS;
   for (int idx = tid; idx < total; idx += GEMV_THREADS) {
-    float v = 0.f;
-    for (int sp = 0; sp < nsplit; ++sp) v += __ldcg(base + (int64_t)sp * total + idx);
+    const float v = sum_partials(base + idx, total, nsplit);
     const int m = idx / SPAN_COLS, lc = idx % SPAN_COLS;
     const int n = span_col<G>(span, lc);
     if (n < N) C[(int64_t)m * ldc + n] = __float2half_rn(v);
@@ -430,8 +445,7 @@ gemv_nk_kernel(const __half* __restrict__ X, int64_t ldx, const uint8_t* __restr
   const int total = M * NK_ROWS;
   const float* base = part + ((int64_t)nblk * nsplit * M) * NK_ROWS;
   for (int idx = tid; idx < total; idx += GEMV_THREADS) {
-    float v = 0.f;
-    for (int sp = 0; sp < nsplit; ++sp) v += __ldcg(base + (int64_t)sp * total + idx);
+    const float v = sum_partials(base + idx, total, nsplit);
     const int m = idx / NK_ROWS, n = nblk * NK_ROWS + idx % NK_ROWS;
     if (n < N) Y[(int64_t)m * ldy + n] = __float2half_rn(v);
   }

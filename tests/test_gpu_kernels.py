@@ -343,3 +343,68 @@ def test_silu_mul_golden(K, golden):
     y = K.silu_mul(dev(golden["ep.silu.a"]), dev(golden["ep.silu.b"]))
     d = np.abs(host(y).view(np.int16).astype(np.int32) - golden["ep.silu.y"].view(np.int16).astype(np.int32))
     assert d.max() <= 1 and (d > 0).mean() < 0.01
+
+
+# ------------------------------------------------------------------------------ decode-step kernels
+def test_rope_kv_append_and_tree_decode(K):
+    """One decode step of the KV-shared model's attention: rotary embedding + Q4_0 append of the
+    new token, then attention over shared prompt + packed Q4_0 suffix + the un-quantised new
+    token; oracle = rope, quantise/dequantise round trip of the older suffix rows, softmax."""
+    from spec_mcts_b200._lib import check, lib
+    rng = np.random.default_rng(11)
+    B, H, Hkv, D, maxB, maxT, maxP, plen, n_pos = 3, 4, 2, 128, 4, 8, 48, 37, 64
+    cos, sin = O.rope_tables(D, n_pos, 1e6)
+    cos_h, sin_h = np.ascontiguousarray(cos[:, :64]), np.ascontiguousarray(sin[:, :64])
+    pk = rng.standard_normal((maxP, Hkv, D)).astype(np.float16)
+    pv = rng.standard_normal((maxP, Hkv, D)).astype(np.float16)
+    kq = torch.zeros((maxB, maxT, Hkv, 64), dtype=torch.int8, device="cuda")
+    ks = torch.zeros((maxB, maxT, Hkv, 2), dtype=torch.float16, device="cuda")
+    vq, vs = torch.zeros_like(kq), torch.zeros_like(ks)
+    plen_d = torch.tensor([plen], dtype=torch.int32, device="cuda")
+    pk_d, pv_d, cos_d, sin_d = dev(pk), dev(pv), dev(cos_h), dev(sin_h)
+    ws = torch.empty(lib.q40_attn_shared_prefix_workspace_bytes(B, H, D, maxP), dtype=torch.uint8, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    hist_k = [[] for _ in range(B)]   # what later steps see: Q4_0 round trip of rotated k, and of v
+    hist_v = [[] for _ in range(B)]
+    for step in range(5):
+        pos = plen + step
+        q = rng.standard_normal((B, H * D)).astype(np.float16)
+        k = rng.standard_normal((B, Hkv * D)).astype(np.float16)
+        v = rng.standard_normal((B, Hkv * D)).astype(np.float16)
+        q_d, k_d, v_d = dev(q), dev(k), dev(v)
+        pos_d = torch.full((maxB,), pos, dtype=torch.int32, device="cuda")
+        check(lib.q40_rope_kv_append(q_d.data_ptr(), H * D, k_d.data_ptr(), Hkv * D, v_d.data_ptr(), Hkv * D,
+                                     pos_d.data_ptr(), plen_d.data_ptr(), cos_d.data_ptr(), sin_d.data_ptr(), n_pos,
+                                     kq.data_ptr(), ks.data_ptr(), vq.data_ptr(), vs.data_ptr(), B, H, Hkv, D, maxT,
+                                     st))
+        o_d = torch.empty((B, H * D), dtype=torch.float16, device="cuda")
+        check(lib.q40_attn_tree_decode(q_d.data_ptr(), pk_d.data_ptr(), pv_d.data_ptr(), maxP, plen_d.data_ptr(),
+                                       pk_d.stride(0), pk_d.stride(1), kq.data_ptr(), ks.data_ptr(), vq.data_ptr(),
+                                       vs.data_ptr(), maxT, pos_d.data_ptr(), k_d.data_ptr(), v_d.data_ptr(),
+                                       Hkv * D, o_d.data_ptr(), B, H, Hkv, D, ws.data_ptr(), ws.numel(), st))
+        # oracle
+        qr = O.apply_rope(q.reshape(B, H, D), cos[pos], sin[pos])
+        kr = O.apply_rope(k.reshape(B, Hkv, D), cos[pos], sin[pos])
+        assert_bits_equal(host(q_d).reshape(B, H, D), qr)
+        assert_bits_equal(host(k_d).reshape(B, Hkv, D), kr)
+        vr = v.reshape(B, Hkv, D)
+        ref = np.zeros((B, H, D), dtype=np.float32)
+        for b in range(B):
+            for h in range(H):
+                g = h // (H // Hkv)
+                Ks = [pk[:plen, g]] + [x[g][None] for x in hist_k[b]] + [kr[b, g][None]]
+                Vs = [pv[:plen, g]] + [x[g][None] for x in hist_v[b]] + [vr[b, g][None]]
+                ref[b, h] = O._softmax_av(qr[b, h], np.concatenate(Ks), np.concatenate(Vs), 1 / np.sqrt(D))
+        assert_close(host(o_d).reshape(B, H, D), ref.astype(np.float16))
+        # the cache rows just written must equal the packer's output for the rotated k and v
+        kq_o, ks_o = O.quantize_q40(kr.reshape(-1, D), 64)
+        vq_o, vs_o = O.quantize_q40(vr.reshape(-1, D), 64)
+        np.testing.assert_array_equal(host(kq[:B, step]).reshape(-1, 64), kq_o)
+        assert_bits_equal(host(ks[:B, step]).reshape(-1, 1), ks_o)
+        np.testing.assert_array_equal(host(vq[:B, step]).reshape(-1, 64), vq_o)
+        assert_bits_equal(host(vs[:B, step]).reshape(-1, 1), vs_o)
+        kd = O.dequantize_q40(kq_o, ks_o, 64, (B, Hkv, D))
+        vd = O.dequantize_q40(vq_o, vs_o, 64, (B, Hkv, D))
+        for b in range(B):
+            hist_k[b].append(kd[b])
+            hist_v[b].append(vd[b])

@@ -63,6 +63,8 @@ def test_small_model_matches_reference_class(small, use_graph):
     for step in range(ref_logits.shape[0]):
         lg = model(toks, pos)[:, -1]
         got = lg.float().cpu().numpy()
+        err = np.abs(got - ref_logits[step].astype(np.float32)).max(axis=-1)
+        print("step", step, "max |logit error| per branch", np.round(err, 3))
         logits_close(got, ref_logits[step])
         am = got.argmax(-1)
         for b in range(B):
