@@ -45,8 +45,20 @@ def logits_close(a, b):
     np.testing.assert_allclose(a.astype(np.float32), b.astype(np.float32), rtol=2e-2, atol=0.15)
 
 
+def rel_l2(a, b):
+    a, b = a.astype(np.float32), b.astype(np.float32)
+    return np.linalg.norm(a - b, axis=-1) / np.linalg.norm(b, axis=-1)
+
+
 @pytest.mark.parametrize("use_graph", [False, True])
 def test_small_model_matches_reference_class(small, use_graph):
+    """Against the reference class's own logits.  The Q4_0 round trip of the KV cache makes the
+    logits discontinuous in their inputs (a 1-ulp difference in k can flip a 4-bit code, a jump
+    of absmax/7), so two correct implementations agree closely on most steps and by a few
+    percent on the steps where a code flipped; the CPU oracle shows the same pattern against
+    the reference (tests/test_oracle_golden.py::test_model_oracle).  Hence: relative L2 error
+    per (step, branch) below 1e-1 with a median below 5e-3, and identical greedy tokens
+    wherever the reference's top-1/top-2 margin exceeds 2.5."""
     g = small
     model = build_model(g, use_graph)
     prompt = torch.from_numpy(g["prompt"]).cuda()
@@ -60,19 +72,52 @@ def test_small_model_matches_reference_class(small, use_graph):
     ref_logits, ref_toks = g["decode_logits"], g["decode_tokens"]
     srt = np.sort(ref_logits.astype(np.float32), axis=-1)
     margin = srt[..., -1] - srt[..., -2]
+    rels = []
     for step in range(ref_logits.shape[0]):
-        lg = model(toks, pos)[:, -1]
-        got = lg.float().cpu().numpy()
-        err = np.abs(got - ref_logits[step].astype(np.float32)).max(axis=-1)
-        print("step", step, "max |logit error| per branch", np.round(err, 3))
-        logits_close(got, ref_logits[step])
+        got = model(toks, pos)[:, -1].float().cpu().numpy()
+        rels.append(rel_l2(got, ref_logits[step]))
         am = got.argmax(-1)
         for b in range(B):
-            if margin[step, b] > 0.2:
+            if margin[step, b] > 2.5:
                 assert am[b] == ref_toks[step, b], (step, b, margin[step, b])
-        # teacher forcing: continue from the reference's tokens so that a near-tie cannot
-        # make the sequences diverge
+        # teacher forcing: continue from the reference's tokens
         toks = torch.from_numpy(ref_toks[step]).view(B, 1).cuda()
+        pos += 1
+    rels = np.array(rels)
+    print("relative L2 error per (step, branch):\n", np.round(rels, 4))
+    assert rels.max() < 1e-1 and np.median(rels) < 5e-3
+
+
+def test_small_model_matches_oracle_with_forced_cache(small):
+    """Against the numpy model oracle, with the oracle's suffix cache overwritten after every
+    step by the rows the GPU wrote (so a flipped 4-bit code cannot make the two histories
+    diverge): every step's logits must then agree within the matmul tolerance."""
+    from oracle import model_oracle as MO
+    from oracle import q40_oracle as O
+    g = small
+    model = build_model(g, True)
+    orc = MO.from_golden(g)
+    prompt = g["prompt"]
+    lg = model(torch.from_numpy(prompt).cuda(), 0)
+    lo = orc.forward(prompt, 0)
+    logits_close(lg[0].cpu().numpy(), lo[0])
+    B = 3
+    model.fork(0, 1, B - 1)
+    orc.fork(0, 1, B - 1)
+    toks = g["first_tokens"]
+    pos = prompt.shape[1]
+    C = model._caches
+    for step in range(10):
+        got = model(torch.from_numpy(toks).cuda(), pos)[:, -1].float().cpu().numpy()
+        ref = orc.forward(toks, pos)[:, 0]
+        logits_close(got, ref)
+        for l in range(2):
+            for b in range(B):
+                kq, ks = C["kq"][l, b, step].cpu().numpy(), C["ks"][l, b, step].cpu().numpy()
+                vq, vs = C["vq"][l, b, step].cpu().numpy(), C["vs"][l, b, step].cpu().numpy()
+                orc.sk[l][b][step] = O.dequantize_q40(kq, ks.reshape(-1, 1), 64, (2, 128))
+                orc.sv[l][b][step] = O.dequantize_q40(vq, vs.reshape(-1, 1), 64, (2, 128))
+        toks = got.argmax(-1).reshape(B, 1)
         pos += 1
 
 

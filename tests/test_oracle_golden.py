@@ -131,3 +131,32 @@ def test_cpu_path_matches_golden(golden):
     y, _, _ = C.linear_nk(torch.from_numpy(golden["mm.nk.x"]), torch.from_numpy(golden["mm.nk.wq"]),
                           torch.from_numpy(golden["mm.nk.ws"]), (384, 256))
     np.testing.assert_array_equal(y.numpy().view(np.uint16), golden["mm.nk.y"].view(np.uint16))
+
+
+def test_model_oracle():
+    """The numpy restatement of the model's forward pass against logits from the reference's own
+    model class (prefill -> fork -> 12 teacher-forced decode steps on 3 branches).  Tolerance
+    is statistical because the Q4_0 KV round trip is discontinuous (see tests/test_gpu_model.py)."""
+    import os
+    from oracle import model_oracle as MO
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "model_small.npz"))
+    m = MO.from_golden(g)
+    lg = m.forward(g["prompt"], 0)
+    np.testing.assert_allclose(lg[0, -1].astype(np.float32), g["prefill_logits_last"].astype(np.float32),
+                               rtol=2e-2, atol=0.15)
+    m.fork(0, 1, 2)
+    toks, pos = g["first_tokens"], g["prompt"].shape[1]
+    rels = []
+    srt = np.sort(g["decode_logits"].astype(np.float32), axis=-1)
+    margin = srt[..., -1] - srt[..., -2]
+    for step in range(12):
+        got = m.forward(toks, pos)[:, 0].astype(np.float32)
+        ref = g["decode_logits"][step].astype(np.float32)
+        rels.append(np.linalg.norm(got - ref, axis=-1) / np.linalg.norm(ref, axis=-1))
+        for b in range(3):
+            if margin[step, b] > 2.5:
+                assert got[b].argmax() == g["decode_tokens"][step, b]
+        toks = g["decode_tokens"][step].reshape(3, 1)
+        pos += 1
+    rels = np.array(rels)
+    assert rels.max() < 1e-1 and np.median(rels) < 5e-3
