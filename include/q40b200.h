@@ -86,6 +86,31 @@ int q40_gemm_nk(const void* x, int64_t ldx, const void* wq, const void* ws, void
                 int64_t ldy, int M, int N, int K, int group, void* workspace,
                 size_t workspace_bytes, void* stream);
 
+/* Decode-step form of q40_gemm_kn (group 64, 1 <= M <= 16, K % 16 == 0, every N % 128 == 0):
+ * one launch computes out[i] = X @ deq(B_i) for nmat (1..3) matrices that share the
+ * activations, with the element-wise neighbours of the matmul folded in.  mode:
+ *   0  X = a                                   out[i] = fp16(acc)
+ *   1  X = RMSNorm(a) (a = residual stream, weight norm_w, eps; the row sums of squares are the
+ *      sums of ss_in[m][0..ss_in_count), as written by a mode-2 launch)      out[i] = fp16(acc)
+ *   2  nmat == 1: out = fp16(h_in + fp16(acc)) (h_in may alias out), and
+ *      ss_out[m][0..ss_out_count) receives partial sums of out^2 (ss_out_count must equal
+ *      q40_gemv_fused_ss_count(N, K, max_cluster))
+ *   3  nmat == 2 (w1, w3), prologue as mode 1:  out[0] = fp16(fp16(silu(fp16(acc1))) * fp16(acc3))
+ * Split-K partials are summed inside a thread-block cluster (max_cluster = 8, or 16 where the
+ * device allows non-portable cluster sizes); no workspace.  With use_pdl != 0 the kernel is
+ * launched with programmatic stream serialization: it prefetches weights before waiting for
+ * the preceding kernel on the stream, so the preceding kernel must not be one whose output
+ * buffers this launch's *weights* alias (they never do).
+ * Replaces: LinearQ4_0.forward chains of TransformerBlock.forward
+ * (hf_model_q40_kv_shared.py:228-236, 313, 409, 431-436, 456-467) together with RMSNorm
+ * (:123-134), the residual adds (:463-466) and F.silu(w1 x) * w3 x (:434). */
+int q40_gemv_fused(int mode, int nmat, const void* const* bw, const void* const* bs, void* const* out,
+                   const int* n_cols, int64_t ldc, const void* a, int64_t lda, int M, int K,
+                   const void* norm_w, const float* ss_in, int ss_in_count, float eps, const void* h_in,
+                   int64_t ldh, float* ss_out, int ss_out_count, int max_cluster, int use_pdl,
+                   void* stream);
+int q40_gemv_fused_ss_count(int N, int K, int max_cluster);
+
 /* ---- decode attention (one query token per branch) ---------------------------------- */
 
 /* q[B,H,D], k/v[B,Hkv,L,D] contiguous fp16 -> o[B,H,D]; scale 1/sqrt(D); D == 128;
@@ -125,7 +150,8 @@ int q40_attn_shared_prefix(const void* q, const void* prefix_k, const void* pref
                            void* stream);
 
 /* One decode step of the KV-shared model's attention, replayable from a CUDA graph because
- * every length is read from device memory: all B branches attend to the shared fp16 prompt
+ * every length is read from device memory (branch b's queries start at q + b*q_stride
+ * elements): all B branches attend to the shared fp16 prompt
  * cache (first *prefix_len_dev <= max_prefix_len keys), then to their own Q4_0 suffix cache
  * (packed rows cache_kq/cache_vq [maxB, max_t, Hkv, 64] bytes with scales cache_ks/cache_vs
  * [maxB, max_t, Hkv, 2] fp16; branch b holds pos_dev[b] - *prefix_len_dev tokens), and
@@ -134,7 +160,7 @@ int q40_attn_shared_prefix(const void* q, const void* prefix_k, const void* pref
  * max_prefix_len.
  * Replaces: the decode branch of Attention.forward (hf_model_q40_kv_shared.py:330-405):
  * dequantise the whole suffix, overwrite the new position, cat with the expanded prompt, SDPA. */
-int q40_attn_tree_decode(const void* q, const void* prefix_k, const void* prefix_v,
+int q40_attn_tree_decode(const void* q, int64_t q_stride, const void* prefix_k, const void* prefix_v,
                          int max_prefix_len, const int32_t* prefix_len_dev,
                          int64_t prefix_key_stride, int64_t prefix_head_stride,
                          const void* cache_kq, const void* cache_ks, const void* cache_vq,
@@ -153,6 +179,13 @@ int q40_rope_kv_append(void* q, int64_t q_stride, void* k, int64_t k_stride, con
                        const void* cos_tbl, const void* sin_tbl, int n_pos, void* cache_kq,
                        void* cache_ks, void* cache_vq, void* cache_vs, int B, int H, int Hkv, int D,
                        int max_t, void* stream);
+
+/* h[r,:] = emb[tokens[r], :] (fp16 table [vocab, dim], int64 ids, ids clamped into the table)
+ * and the row's sum of squares as ss[r][0] (ss[r][1..ss_count) = 0): the first producer of the
+ * residual stream in the form q40_gemv_fused mode 1/3 consumes.
+ * Replaces: tok_embeddings lookup in Transformer.forward (hf_model_q40_kv_shared.py:495-498). */
+int q40_embed_rows(const void* emb, const int64_t* tokens, void* h, float* ss, int ss_count, int rows,
+                   int dim, int vocab, void* stream);
 
 /* ---- epilogue math with the reference's rounding points ------------------------------ */
 

@@ -44,6 +44,10 @@ SIGNATURES = {
                             c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "q40_gemm_nk": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
                             c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "q40_gemv_fused": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
+                               c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int64, c_void_p,
+                               c_int, c_int, c_int, c_void_p]),
+    "q40_gemv_fused_ss_count": (c_int, [c_int, c_int, c_int]),
     "q40_attn_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p]),
     "q40_attn_paged": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -52,13 +56,14 @@ SIGNATURES = {
     "q40_attn_shared_prefix": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64,
                                        c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                        c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
-    "q40_attn_tree_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64,
+    "q40_attn_tree_decode": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64,
                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                      c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                      c_size_t, c_void_p]),
     "q40_rope_kv_append": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
                                    c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "q40_embed_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "q40_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
                             c_void_p]),
     "q40_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64,

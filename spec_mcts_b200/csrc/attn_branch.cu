@@ -45,6 +45,7 @@ template <int MODE>
 __global__ void __launch_bounds__(BR_THREADS)
 attn_branch_kernel(const BranchArgs a) {
   constexpr int D = ATTN_D;
+  asm volatile("griddepcontrol.launch_dependents;");   // a dependent may start prefetching its weights
   const int bh = blockIdx.x;
   const int b = bh / a.H, h = bh % a.H;
   const int hk = h / (a.H / a.Hkv);
@@ -63,7 +64,7 @@ attn_branch_kernel(const BranchArgs a) {
   // this lane's 16 query dims, pre-multiplied by scale*log2(e)
   float qf[16];
   {
-    const __half* qp = a.q + ((int64_t)b * a.H + h) * D + sub * 16;
+    const __half* qp = a.q + (int64_t)b * a.q_stride + h * D + sub * 16;
     const uint4 q0 = *reinterpret_cast<const uint4*>(qp);
     const uint4 q1 = *reinterpret_cast<const uint4*>(qp + 8);
     const __half2* h0 = reinterpret_cast<const __half2*>(&q0);
@@ -301,7 +302,7 @@ extern "C" int q40_attn_decode(const void* q, const void* k, const void* v, void
   if (!q40_aligned(q, 16) || !q40_aligned(k, 16) || !q40_aligned(v, 16) || !q40_aligned(o, 2))
     return Q40_E_ALIGN;
   q40::BranchArgs a{};
-  a.q = (const __half*)q; a.k = (const __half*)k; a.v = (const __half*)v; a.o = (__half*)o;
+  a.q = (const __half*)q; a.q_stride = (int64_t)H * D; a.k = (const __half*)k; a.v = (const __half*)v; a.o = (__half*)o;
   a.L = L; a.H = H; a.Hkv = Hkv; a.P = 0; a.page_size = 1;
   a.scale_log2 = q40::attn_scale_log2(D);
   return q40::launch_branch(a, 0, B, (cudaStream_t)stream);
@@ -321,7 +322,7 @@ extern "C" int q40_attn_paged(const void* page_tbl, int idx_bytes, int64_t tbl_s
   if (B == 0) return Q40_OK;
   if (!q40_aligned(q, 16) || !q40_aligned(kpool, 16) || !q40_aligned(vpool, 16)) return Q40_E_ALIGN;
   q40::BranchArgs a{};
-  a.q = (const __half*)q; a.k = (const __half*)kpool; a.v = (const __half*)vpool; a.o = (__half*)o;
+  a.q = (const __half*)q; a.q_stride = (int64_t)H * D; a.k = (const __half*)kpool; a.v = (const __half*)vpool; a.o = (__half*)o;
   a.tbl = page_tbl; a.tbl_stride = tbl_stride; a.seq_lens = seq_lens;
   a.L = Lmax; a.H = H; a.Hkv = Hkv; a.P = P; a.page_size = page_size;
   a.scale_log2 = q40::attn_scale_log2(D);

@@ -9,7 +9,8 @@ constexpr int ATTN_D = 128;  // head dim of every supported model (CodeLlama 7B/
 inline float attn_scale_log2(int D) { return (1.0f / sqrtf((float)D)) * 1.4426950408889634f; }
 
 struct BranchArgs {
-  const __half* q;        // [B, H, D]
+  const __half* q;        // branch b, head h at q + b*q_stride + h*D
+  int64_t q_stride;
   const __half* k;        // contiguous: [B,Hkv,L,D]; paged: pool [Hkv,P,D]
   const __half* v;
   __half* o;              // [B, H, D]

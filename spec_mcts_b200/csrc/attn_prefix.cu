@@ -25,7 +25,8 @@ constexpr int PF_ROW_BYTES = ATTN_D * 2;       // 256 B per key
 constexpr int PF_TILE_BYTES = PF_KT * PF_ROW_BYTES;  // 16 KB
 
 struct PrefixArgs {
-  const __half* q;    // [B, H, D]
+  const __half* q;    // branch b, head h at q + b*q_stride + h*D
+  int64_t q_stride;
   const __half* pk;   // key t of kv head h at pk + t*key_stride + h*head_stride
   const __half* pv;
   float* pm;          // [nsp][B*H]
@@ -84,6 +85,7 @@ attn_prefix_kernel(const PrefixArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   // [stage][K tile | V tile]; the Q rows are staged through the same memory first
   const uint32_t sbase = smem_u32(smem);
+  asm volatile("griddepcontrol.launch_dependents;");   // a dependent may start prefetching its weights
 
   const int sp = blockIdx.x, hk = blockIdx.y, rblk = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -102,7 +104,7 @@ attn_prefix_kernel(const PrefixArgs a) {
     const int gr = row0 + r;
     const bool ok = gr < rows;
     const int b = ok ? gr / rep : 0, j = ok ? gr % rep : 0;
-    const __half* src = a.q + ((int64_t)b * a.H + hk * rep + j) * D + ch * 8;
+    const __half* src = a.q + (int64_t)b * a.q_stride + (hk * rep + j) * D + ch * 8;
     cp_async16(sbase + tile_off(r, ch), src, ok);
   }
   cp_async_commit();
@@ -316,7 +318,7 @@ extern "C" int q40_attn_shared_prefix(const void* q, const void* prefix_k, const
   const int64_t rows_total = (int64_t)B * H;
 
   BranchArgs br{};
-  br.q = (const __half*)q; br.k = (const __half*)kpool; br.v = (const __half*)vpool; br.o = (__half*)o;
+  br.q = (const __half*)q; br.q_stride = (int64_t)H * D; br.k = (const __half*)kpool; br.v = (const __half*)vpool; br.o = (__half*)o;
   br.tbl = page_tbl; br.tbl_stride = tbl_stride; br.seq_lens = seq_lens;
   br.L = Lmax; br.H = H; br.Hkv = Hkv; br.P = P; br.page_size = page_size;
   br.scale_log2 = attn_scale_log2(D);
@@ -330,7 +332,7 @@ extern "C" int q40_attn_shared_prefix(const void* q, const void* prefix_k, const
     float* pm = po + (size_t)nsp * rows_total * D;
     float* pl = pm + (size_t)nsp * rows_total;
     PrefixArgs pa{};
-    pa.q = (const __half*)q; pa.pk = (const __half*)prefix_k; pa.pv = (const __half*)prefix_v;
+    pa.q = (const __half*)q; pa.q_stride = (int64_t)H * D; pa.pk = (const __half*)prefix_k; pa.pv = (const __half*)prefix_v;
     pa.pm = pm; pa.pl = pl; pa.po = po;
     pa.key_stride = prefix_key_stride; pa.head_stride = prefix_head_stride;
     pa.B = B; pa.H = H; pa.Hkv = Hkv; pa.prefix_len = prefix_len;
@@ -345,7 +347,7 @@ extern "C" int q40_attn_shared_prefix(const void* q, const void* prefix_k, const
   return launch_branch(br, mode, B, st);
 }
 
-extern "C" int q40_attn_tree_decode(const void* q, const void* prefix_k, const void* prefix_v,
+extern "C" int q40_attn_tree_decode(const void* q, int64_t q_stride, const void* prefix_k, const void* prefix_v,
                                     int max_prefix_len, const int32_t* prefix_len_dev,
                                     int64_t prefix_key_stride, int64_t prefix_head_stride,
                                     const void* cache_kq, const void* cache_ks, const void* cache_vq,
@@ -359,7 +361,9 @@ extern "C" int q40_attn_tree_decode(const void* q, const void* prefix_k, const v
   if ((cur_k == nullptr) != (cur_v == nullptr)) return Q40_E_NULL;
   if (D != ATTN_D) return Q40_E_UNSUPPORTED;
   if (B < 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0 || max_prefix_len <= 0 || max_t <= 0) return Q40_E_SHAPE;
-  if (prefix_key_stride % 8 != 0 || prefix_head_stride % 8 != 0 || cur_stride % 8 != 0) return Q40_E_ALIGN;
+  if (prefix_key_stride % 8 != 0 || prefix_head_stride % 8 != 0 || cur_stride % 8 != 0 || q_stride % 8 != 0)
+    return Q40_E_ALIGN;
+  if (q_stride < (int64_t)H * D) return Q40_E_SHAPE;
   if (B == 0) return Q40_OK;
   if (!q40_aligned(q, 16) || !q40_aligned(prefix_k, 16) || !q40_aligned(prefix_v, 16) ||
       !q40_aligned(cache_kq, 16) || !q40_aligned(cache_vq, 16) || !q40_aligned(cur_k, 16) ||
@@ -375,7 +379,7 @@ extern "C" int q40_attn_tree_decode(const void* q, const void* prefix_k, const v
   float* pm = po + (size_t)nsp * rows_total * D;
   float* pl = pm + (size_t)nsp * rows_total;
   PrefixArgs pa{};
-  pa.q = (const __half*)q; pa.pk = (const __half*)prefix_k; pa.pv = (const __half*)prefix_v;
+  pa.q = (const __half*)q; pa.q_stride = q_stride; pa.pk = (const __half*)prefix_k; pa.pv = (const __half*)prefix_v;
   pa.pm = pm; pa.pl = pl; pa.po = po;
   pa.key_stride = prefix_key_stride; pa.head_stride = prefix_head_stride;
   pa.prefix_len_dev = prefix_len_dev;
@@ -384,7 +388,7 @@ extern "C" int q40_attn_tree_decode(const void* q, const void* prefix_k, const v
   int rc = launch_prefix(pa, nsp, st);
   if (rc != Q40_OK) return rc;
   BranchArgs br{};
-  br.q = (const __half*)q; br.o = (__half*)o;
+  br.q = (const __half*)q; br.q_stride = q_stride; br.o = (__half*)o;
   br.H = H; br.Hkv = Hkv; br.L = max_t;
   br.scale_log2 = pa.scale_log2;
   br.pm = pm; br.pl = pl; br.po = po; br.nsp = nsp;

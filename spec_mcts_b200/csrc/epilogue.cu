@@ -13,6 +13,7 @@ rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ residual
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __half* row = reinterpret_cast<__half*>(smem_raw);  // [dim]
   __shared__ float red[8];
+  asm volatile("griddepcontrol.launch_dependents;");   // a dependent may start prefetching its weights
   const int r = blockIdx.x, tid = threadIdx.x;
   const __half* xr = x + (int64_t)r * dim;
   const __half* rr = residual ? residual + (int64_t)r * dim : nullptr;
@@ -103,7 +104,53 @@ silu_mul_kernel(const __half* __restrict__ a, const __half* __restrict__ b, __ha
   }
 }
 
+// One CTA per row: h[r] = emb[token[r]] and the row's sum of squares in ss[r][0] (ss[r][1..] = 0),
+// the form in which the fused decode matmuls expect it.
+__global__ void __launch_bounds__(256)
+embed_rows_kernel(const __half* __restrict__ emb, const int64_t* __restrict__ tokens, __half* __restrict__ h,
+                  float* __restrict__ ss, int ss_count, int dim, int vocab) {
+  __shared__ float red[8];
+  asm volatile("griddepcontrol.launch_dependents;");
+  const int r = blockIdx.x, tid = threadIdx.x;
+  int64_t tok = tokens[r];
+  tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+  const __half* src = emb + tok * dim;
+  float s = 0.f;
+  for (int i = tid * 8; i < dim; i += blockDim.x * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(src + i);
+    *reinterpret_cast<uint4*>(h + (int64_t)r * dim + i) = v;
+    const __half2* vh = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(vh[j]);
+      s = fmaf(f.x, f.x, s);
+      s = fmaf(f.y, f.y, s);
+    }
+  }
+  s = warp_sum(s);
+  if ((tid & 31) == 0) red[tid >> 5] = s;
+  __syncthreads();
+  for (int i = tid; i < ss_count; i += blockDim.x) {
+    float tot = 0.f;
+    if (i == 0)
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
+    ss[(int64_t)r * ss_count + i] = tot;
+  }
+}
+
 }  // namespace q40
+
+extern "C" int q40_embed_rows(const void* emb, const int64_t* tokens, void* h, float* ss, int ss_count,
+                              int rows, int dim, int vocab, void* stream) {
+  if (!emb || !tokens || !h || !ss) return Q40_E_NULL;
+  if (rows < 0 || dim <= 0 || dim % 8 != 0 || vocab <= 0 || ss_count < 1) return Q40_E_SHAPE;
+  if (rows == 0) return Q40_OK;
+  if (!q40_aligned(emb, 16) || !q40_aligned(h, 16)) return Q40_E_ALIGN;
+  q40::embed_rows_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>((const __half*)emb, tokens, (__half*)h, ss,
+                                                              ss_count, dim, vocab);
+  Q40_LAUNCH_CHECK();
+  return Q40_OK;
+}
 
 extern "C" int q40_rmsnorm(const void* x, const void* residual, const void* w, void* y, void* h_out,
                            int rows, int dim, float eps, void* stream) {

@@ -49,6 +49,7 @@ __global__ void __launch_bounds__(64)
 rope_kv_append_kernel(const AppendArgs a) {
   constexpr int D = 128, HD = 64;
   __shared__ float red[2];
+  asm volatile("griddepcontrol.launch_dependents;");   // a dependent may start prefetching its weights
   const int b = blockIdx.x, hh = blockIdx.y, d = threadIdx.x;
   int p = a.pos[b];
   p = min(max(p, 0), a.n_pos - 1);

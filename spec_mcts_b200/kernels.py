@@ -22,6 +22,7 @@ __all__ = [
     "quantize_q40", "dequantize_q40", "triton_deq_int40", "triton_q_int40", "triton_q_int40_sliced",
     "quantize_q40_rows", "matmul", "matmul_q40", "linear_q40", "flash_attn", "page_flash_attn",
     "triton_attn", "chunk_attn", "shared_prefix_attn", "matmul_split_k", "rmsnorm", "rope_", "silu_mul",
+    "gemv_fused", "embed_rows",
     "Q40Error",
 ]
 
@@ -195,6 +196,61 @@ def linear_q40(x: torch.Tensor, w_q: torch.Tensor, w_s: torch.Tensor, w_shape, *
                               w_s.contiguous().data_ptr(), y.data_ptr(), y.stride(0), M, N, K,
                               group_size, ws.data_ptr(), ws.numel(), _stream(dev)), "q40_gemm_nk")
     return y.view(*lead, N)
+
+
+def gemv_fused(mode: int, a: torch.Tensor, weights, *, norm_w=None, ss_in=None, eps: float = 1e-5, h_in=None,
+               max_cluster: int = 16, use_pdl: bool = False):
+    """Decode-step matmul(s) with fused neighbours (q40_gemv_fused in include/q40b200.h).
+    `weights` is a list of 1-3 (b_w, b_s, (K, N)) triples sharing the activations a [M <= 16, K].
+    mode 0: [a @ deq(B_i)]; 1: RMSNorm(a; norm_w, ss_in) first; 2: returns (h_in + a @ deq(B),
+    ss_out [M, count]); 3: silu(RMSNorm(a) @ deq(B_0)) * (RMSNorm(a) @ deq(B_1))."""
+    import ctypes
+    dev = _need_cuda(a, norm_w, ss_in, h_in, *[w[0] for w in weights], *[w[1] for w in weights])
+    M, K = a.shape
+    n = len(weights)
+    Ns = [int(w[2][1]) for w in weights]
+    for w in weights:
+        assert int(w[2][0]) == K
+    P = ctypes.c_void_p * n
+    if mode == 3:
+        outs = [torch.empty((M, Ns[0]), dtype=torch.float16, device=dev)] * 2
+    else:
+        outs = [torch.empty((M, N), dtype=torch.float16, device=dev) for N in Ns]
+    ldc = max(Ns)
+    if mode in (0, 1) and n > 1:
+        # the C entry takes one leading dimension: give the outputs a common row pitch
+        buf = torch.empty((M, sum(Ns)), dtype=torch.float16, device=dev)
+        outs, c0 = [], 0
+        for N in Ns:
+            outs.append(buf[:, c0:c0 + N])
+            c0 += N
+        ldc = sum(Ns)
+    ss_out, cnt = None, 0
+    if mode == 2:
+        cnt = lib.q40_gemv_fused_ss_count(Ns[0], K, max_cluster)
+        ss_out = torch.empty((M, cnt), dtype=torch.float32, device=dev)
+    a = a.contiguous()
+    check(lib.q40_gemv_fused(mode, n, P(*[w[0].data_ptr() for w in weights]), P(*[w[1].data_ptr() for w in weights]),
+                             P(*[o.data_ptr() for o in outs]), (ctypes.c_int * n)(*Ns), ldc, a.data_ptr(),
+                             a.stride(0), M, K, _ptr(norm_w), _ptr(ss_in), ss_in.shape[1] if ss_in is not None else 0,
+                             float(eps), _ptr(h_in), h_in.stride(0) if h_in is not None else 0, _ptr(ss_out), cnt,
+                             max_cluster, 1 if use_pdl else 0, _stream(dev)), "q40_gemv_fused")
+    if mode == 2:
+        return outs[0], ss_out
+    if mode == 3:
+        return outs[0]
+    return outs
+
+
+def embed_rows(emb: torch.Tensor, tokens: torch.Tensor, ss_count: int):
+    """h = emb[tokens] plus the per-row sum of squares in the layout gemv_fused modes 1/3 read."""
+    dev = _need_cuda(emb, tokens)
+    rows, dim = tokens.numel(), emb.shape[1]
+    h = torch.empty((rows, dim), dtype=torch.float16, device=dev)
+    ss = torch.empty((rows, ss_count), dtype=torch.float32, device=dev)
+    check(lib.q40_embed_rows(emb.data_ptr(), tokens.to(torch.int64).contiguous().data_ptr(), h.data_ptr(),
+                             ss.data_ptr(), ss_count, rows, dim, emb.shape[0], _stream(dev)), "q40_embed_rows")
+    return h, ss
 
 
 def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = ""):

@@ -194,6 +194,10 @@ class Transformer(nn.Module):
         # kernels of this library enqueued by one decode step (per layer: 2 norms, 7 matmuls,
         # rope+append, 2 attention, SiLU-mul; plus the final norm)
         self.launches_per_step = params.n_layers * 13 + 1
+        # B <= 16 uses the fused, cluster-reduced, dependent-launch-chained matmuls
+        self.use_fused = True
+        self.use_pdl = True
+        self.max_cluster = 16
 
     # ------------------------------------------------------------------ reference API
     @torch.inference_mode()
@@ -273,7 +277,9 @@ class Transformer(nn.Module):
                      ao=e(B, H * D), o=e(B, p.dim), a1=e(B, hid), a3=e(B, hid), g=e(B, hid), f=e(B, p.dim),
                      attn_ws=torch.empty(nb_attn, dtype=torch.uint8, device=dev),
                      gemm_ws=torch.zeros(nb_gemm, dtype=torch.uint8, device=dev),
-                     logits=e(B, p.vocab_size))
+                     logits=e(B, p.vocab_size), qkv=e(B, (H + 2 * Hkv) * D),
+                     ss_attn=torch.zeros((B, 1024), dtype=torch.float32, device=dev),
+                     ss_ffn=torch.zeros((B, 1024), dtype=torch.float32, device=dev))
             self._bufs[B] = b
         return b
 
@@ -286,6 +292,76 @@ class Transformer(nn.Module):
 
     def _decode_body(self, B):
         """Enqueue one decode step for B branches on the current stream (captured into a graph)."""
+        if self.use_fused and B <= 16:
+            return self._decode_body_fused(B)
+        return self._decode_body_unfused(B)
+
+    def _fused(self, mode, lins, outs, ldc, a, lda, M, norm_w=None, ss_in=None, ss_in_count=0, h_in=None,
+               ldh=0, ss_out=None, ss_out_count=0, st=None):
+        import ctypes
+        n = len(lins)
+        P = ctypes.c_void_p * n
+        bw = P(*[l.w.data_ptr() for l in lins])
+        bs = P(*[l.s.data_ptr() for l in lins])
+        op = P(*[o.data_ptr() for o in outs])
+        nc = (ctypes.c_int * n)(*[l.kn()[1] for l in lins])
+        Kd = lins[0].kn()[0]
+        check(lib.q40_gemv_fused(mode, n, bw, bs, op, nc, ldc, a.data_ptr(), lda, M, Kd,
+                                 norm_w.data_ptr() if norm_w is not None else None,
+                                 ss_in.data_ptr() if ss_in is not None else None, ss_in_count,
+                                 float(self.params.norm_eps), h_in.data_ptr() if h_in is not None else None, ldh,
+                                 ss_out.data_ptr() if ss_out is not None else None, ss_out_count,
+                                 self.max_cluster, 1 if self.use_pdl else 0, st), "q40_gemv_fused")
+
+    def _decode_body_fused(self, B):
+        """Decode step for B <= 16 branches: 7 launches per layer (qkv with RMSNorm prologue,
+        rope+append, 2 attention, wo with residual epilogue, w1/w3 with RMSNorm prologue and
+        SiLU-mul epilogue, w2 with residual epilogue), chained with programmatic dependent launch."""
+        p, bufs = self.params, self._step_buffers(B)
+        H, Hkv, D = p.n_heads, self._Hkv, self._D
+        self._check_loaded()
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        hid = self.layers[0].feed_forward.hidden_dim
+        c_attn = lib.q40_gemv_fused_ss_count(p.dim, H * D, self.max_cluster)    # written by wo
+        c_ffn = lib.q40_gemv_fused_ss_count(p.dim, hid, self.max_cluster)       # written by w2
+        h, qkv, ao, gbuf = bufs["h"], bufs["qkv"], bufs["ao"], bufs["g"]
+        ss_attn, ss_ffn = bufs["ss_attn"], bufs["ss_ffn"]
+        W = (H + 2 * Hkv) * D
+        q, k, v = qkv[:, :H * D], qkv[:, H * D:(H + Hkv) * D], qkv[:, (H + Hkv) * D:]
+        pos, plen, aws = self._pos_dev, self._prefix_len_dev, bufs["attn_ws"]
+        check(lib.q40_embed_rows(self.tok_embeddings.weight.data_ptr(), self._tok_dev.data_ptr(), h.data_ptr(),
+                                 ss_ffn.data_ptr(), c_ffn, B, p.dim, p.vocab_size, st), "q40_embed_rows")
+        for layer in self.layers:
+            att, ff = layer.attention, layer.feed_forward
+            self._fused(1, [att.wq, att.wk, att.wv], [q, k, v], W, h, p.dim, B,
+                        norm_w=layer.attention_norm.weight, ss_in=ss_ffn, ss_in_count=c_ffn, st=st)
+            check(lib.q40_rope_kv_append(q.data_ptr(), W, k.data_ptr(), W, v.data_ptr(), W, pos.data_ptr(),
+                                         plen.data_ptr(), self._cos.data_ptr(), self._sin.data_ptr(), self._n_pos,
+                                         att.cache_k.data_ptr(), att.cache_k_s.data_ptr(),
+                                         att.cache_v.data_ptr(), att.cache_v_s.data_ptr(), B, H, Hkv, D,
+                                         p.max_seq_len, st), "q40_rope_kv_append")
+            pk, pv = att.cache_prompt_k, att.cache_prompt_v
+            check(lib.q40_attn_tree_decode(q.data_ptr(), W, pk.data_ptr(), pv.data_ptr(), p.max_prompt_seq_len,
+                                           plen.data_ptr(), pk.stride(0), pk.stride(1), att.cache_k.data_ptr(),
+                                           att.cache_k_s.data_ptr(), att.cache_v.data_ptr(),
+                                           att.cache_v_s.data_ptr(), p.max_seq_len, pos.data_ptr(), k.data_ptr(),
+                                           v.data_ptr(), W, ao.data_ptr(), B, H, Hkv, D, aws.data_ptr(),
+                                           aws.numel(), st), "q40_attn_tree_decode")
+            self._fused(2, [att.wo], [h], p.dim, ao, H * D, B, h_in=h, ldh=p.dim, ss_out=ss_attn,
+                        ss_out_count=c_attn, st=st)
+            self._fused(3, [ff.w1, ff.w3], [gbuf, gbuf], hid, h, p.dim, B, norm_w=layer.ffn_norm.weight,
+                        ss_in=ss_attn, ss_in_count=c_attn, st=st)
+            self._fused(2, [ff.w2], [h], p.dim, gbuf, hid, B, h_in=h, ldh=p.dim, ss_out=ss_ffn,
+                        ss_out_count=c_ffn, st=st)
+        self._norm(h, None, self.norm.weight, bufs["xn"], st)
+        torch.matmul(bufs["xn"], self.output.weight.t(), out=bufs["logits"])
+        if self.greedy_feedback:
+            self._tok_dev[:B].copy_(bufs["logits"].argmax(dim=-1))
+            self._pos_dev[:B] += 1
+        return bufs["logits"]
+
+    def _decode_body_unfused(self, B):
+        """One launch per operation; serves any batch width."""
         p, bufs = self.params, self._step_buffers(B)
         H, Hkv, D = p.n_heads, self._Hkv, self._D
         self._check_loaded()
@@ -308,7 +384,7 @@ class Transformer(nn.Module):
                                          att.cache_v.data_ptr(), att.cache_v_s.data_ptr(), B, H, Hkv, D,
                                          p.max_seq_len, st), "q40_rope_kv_append")
             pk, pv = att.cache_prompt_k, att.cache_prompt_v
-            check(lib.q40_attn_tree_decode(bufs["q"].data_ptr(), pk.data_ptr(), pv.data_ptr(),
+            check(lib.q40_attn_tree_decode(bufs["q"].data_ptr(), H * D, pk.data_ptr(), pv.data_ptr(),
                                            p.max_prompt_seq_len, plen.data_ptr(), pk.stride(0), pk.stride(1),
                                            att.cache_k.data_ptr(), att.cache_k_s.data_ptr(),
                                            att.cache_v.data_ptr(), att.cache_v_s.data_ptr(), p.max_seq_len,
@@ -355,16 +431,26 @@ class Transformer(nn.Module):
     def decode_replay(self, B):
         """Run one decode step for B branches with the tokens/positions already in the device
         buffers (`_tok_dev`, `_pos_dev`); returns the static logits buffer [B, vocab]."""
+        fused = self.use_fused and B <= 16
+        self.launches_per_step = self.params.n_layers * (7 if fused else 13) + (2 if fused else 1)
         if not self.use_cuda_graph:
             return self._decode_body(B)
-        key = (B, self.greedy_feedback)
+        key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster)
         g = self._graphs.get(key)
         if g is None:
             # torch requires capture on a side stream after a warm-up run
             s = torch.cuda.Stream(self.device)
             s.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(s):
-                self._decode_body(B)
+                try:
+                    self._decode_body(B)
+                except K.Q40Error:
+                    if not (fused and self.max_cluster == 16):
+                        raise
+                    # this device cannot schedule 16-CTA clusters: use the portable size
+                    self.max_cluster = 8
+                    key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster)
+                    self._decode_body(B)
             torch.cuda.current_stream(self.device).wait_stream(s)
             torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()

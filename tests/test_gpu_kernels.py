@@ -378,7 +378,7 @@ def test_rope_kv_append_and_tree_decode(K):
                                      kq.data_ptr(), ks.data_ptr(), vq.data_ptr(), vs.data_ptr(), B, H, Hkv, D, maxT,
                                      st))
         o_d = torch.empty((B, H * D), dtype=torch.float16, device="cuda")
-        check(lib.q40_attn_tree_decode(q_d.data_ptr(), pk_d.data_ptr(), pv_d.data_ptr(), maxP, plen_d.data_ptr(),
+        check(lib.q40_attn_tree_decode(q_d.data_ptr(), H * D, pk_d.data_ptr(), pv_d.data_ptr(), maxP, plen_d.data_ptr(),
                                        pk_d.stride(0), pk_d.stride(1), kq.data_ptr(), ks.data_ptr(), vq.data_ptr(),
                                        vs.data_ptr(), maxT, pos_d.data_ptr(), k_d.data_ptr(), v_d.data_ptr(),
                                        Hkv * D, o_d.data_ptr(), B, H, Hkv, D, ws.data_ptr(), ws.numel(), st))
