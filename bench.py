@@ -159,6 +159,13 @@ def build_model(device):
     model = Transformer(args, device=device)
     random_init_(model, seed=0)
     model = model.to(device, torch.float16)
+    # tuning switches for experiments (defaults are what the library ships with)
+    if "Q40_FUSED" in os.environ:
+        model.use_fused = os.environ["Q40_FUSED"] != "0"
+    if "Q40_PDL" in os.environ:
+        model.use_pdl = os.environ["Q40_PDL"] != "0"
+    if "Q40_CLUSTER" in os.environ:
+        model.max_cluster = int(os.environ["Q40_CLUSTER"])
     return model
 
 

@@ -127,16 +127,19 @@ gemv_fused_kernel(const FusedParams p) {
   const uint8_t* wcol = pr.bw + (col_ok ? colbyte : 0);
   const __half* scol = pr.bs + (col_ok ? 2 * (colbyte >> 6) : 0);
 
-  // queue one 16-row step: this lane's 16 bytes of rows k0 .. k0+3 and their scale pairs
-  auto issue = [&](int step, int slot) {
-    const int k0 = kb + step * 16 + 4 * t;
-    const uint32_t base = ring_u32 + slot * F_SLOT_BYTES;
+  // queue one 16-row step: this lane's 16 bytes of rows k0 .. k0+3 and their scale pairs.
+  // K and the split size are multiples of 16, so a step inside the range is never partial.
+  const uint8_t* wstep = wcol + (int64_t)(kb + warp * 16 + 4 * t) * w_ld;   // this warp's step 0
+  const __half* sstep = scol + (int64_t)(kb + warp * 16 + 4 * t) * s_ld;
+  const int64_t w_adv = (int64_t)FW * 16 * w_ld, s_adv = (int64_t)FW * 16 * s_ld;
+  auto issue = [&](int j, int slot) {      // j-th step of this warp
+    const uint32_t base = ring_u32 + slot * F_SLOT_BYTES + lane * 16;
+    const uint8_t* wp = wstep + j * w_adv;
+    const __half* sp = sstep + j * s_adv;
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      const bool ok = col_ok && (k0 + r) < ke;
-      const int64_t k = ok ? (k0 + r) : kb;
-      f_cp16(base + (r * 32 + lane) * 16, wcol + k * w_ld, ok);
-      f_cp4(base + F_SLOT_W + (r * 32 + lane) * 4, scol + k * s_ld, ok);
+      f_cp16(base + r * 512, wp + r * w_ld, col_ok);
+      f_cp4(base + F_SLOT_W - lane * 12 + r * 128, sp + r * s_ld, col_ok);
     }
   };
 
@@ -145,46 +148,58 @@ gemv_fused_kernel(const FusedParams p) {
   const int my_steps = (nsteps > warp) ? (nsteps - warp + FW - 1) / FW : 0;
 #pragma unroll
   for (int j = 0; j < F_DEPTH; ++j) {
-    if (j < my_steps) issue(warp + j * FW, j);
+    if (j < my_steps) issue(j, j);
     f_commit();
   }
   asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  // ---- activations of this k range (optionally RMS-normalised) ----
-  if (PRO == PRO_NORM) {
-    for (int m = warp; m < p.M; m += FW) {
-      float s = 0.f;
-      for (int i = lane; i < p.ss_in_count; i += 32) s += p.ss_in[(int64_t)m * p.ss_in_count + i];
-      s = warp_sum(s);
-      if (lane == 0) s_inv[m] = rsqrtf(s / (float)p.K + p.eps);
-    }
-    __syncthreads();
-  }
+  // ---- activations of this k range: raw copy first (and the norm weights), so that the loads do
+  // not wait for the row statistics; then, for the RMSNorm prologue, normalise in place ----
+  __half* wn = reinterpret_cast<__half*>(s_inv + 16);     // [rows_per_split] norm weights of this range
   {
     const int chunks = p.rows_per_split / 8;
     for (int idx = tid; idx < MT * 8 * chunks; idx += FT) {
       const int m = idx / chunks, kk = (idx % chunks) * 8;
       uint4 v = make_uint4(0, 0, 0, 0);
       const int k = kb + kk;
-      if (m < p.M && k < ke) {        // K is a multiple of 8, so a chunk is never partial
-        v = *reinterpret_cast<const uint4*>(p.a + (int64_t)m * p.lda + k);
-        if (PRO == PRO_NORM) {
-          const uint4 wv = *reinterpret_cast<const uint4*>(p.norm_w + k);
-          __half2* vh = reinterpret_cast<__half2*>(&v);
-          const __half2* wh = reinterpret_cast<const __half2*>(&wv);
-          const float inv = s_inv[m];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = __half22float2(vh[j]);
-            vh[j] = __hmul2(__floats2half2_rn(f.x * inv, f.y * inv), wh[j]);
-          }
-        }
-      }
+      if (m < p.M && k < ke) v = *reinterpret_cast<const uint4*>(p.a + (int64_t)m * p.lda + k);
       *reinterpret_cast<uint4*>(xs + m * xs_ld + kk) = v;
+    }
+    if (PRO == PRO_NORM) {
+      for (int idx = tid; idx < chunks; idx += FT) {
+        const int k = kb + idx * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (k < ke) v = *reinterpret_cast<const uint4*>(p.norm_w + k);
+        *reinterpret_cast<uint4*>(wn + idx * 8) = v;
+      }
+      for (int m = warp; m < p.M; m += FW) {
+        float s = 0.f;
+        for (int i = lane; i < p.ss_in_count; i += 32) s += p.ss_in[(int64_t)m * p.ss_in_count + i];
+        s = warp_sum(s);
+        if (lane == 0) s_inv[m] = rsqrtf(s / (float)p.K + p.eps);
+      }
     }
   }
   __syncthreads();
+  if (PRO == PRO_NORM) {
+    const int chunks = p.rows_per_split / 8;
+    for (int idx = tid; idx < p.M * chunks; idx += FT) {
+      const int m = idx / chunks, kk = (idx % chunks) * 8;
+      uint4 v = *reinterpret_cast<const uint4*>(xs + m * xs_ld + kk);
+      const uint4 wv = *reinterpret_cast<const uint4*>(wn + kk);
+      __half2* vh = reinterpret_cast<__half2*>(&v);
+      const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+      const float inv = s_inv[m];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(vh[j]);
+        vh[j] = __hmul2(__floats2half2_rn(f.x * inv, f.y * inv), wh[j]);
+      }
+      *reinterpret_cast<uint4*>(xs + m * xs_ld + kk) = v;
+    }
+    __syncthreads();
+  }
 
   float acc[MT][16][4];
 #pragma unroll
@@ -238,7 +253,7 @@ gemv_fused_kernel(const FusedParams p) {
     }
     // each lane reads back only what it copied itself and has consumed it by now, so the slot can
     // be refilled without a barrier
-    if (j + F_DEPTH < my_steps) issue(warp + (j + F_DEPTH) * FW, slot);
+    if (j + F_DEPTH < my_steps) issue(j + F_DEPTH, slot);
     f_commit();
   }
   f_wait<0>();
@@ -282,14 +297,23 @@ gemv_fused_kernel(const FusedParams p) {
     for (int cidx = lane; cidx < slice; cidx += 32) {
       const int lc = rank * slice + cidx;
       const int idx = m * F_SPAN_COLS + lc;
+      // all remote loads are issued before the first add; the adds keep rank order
       float v0 = 0.f, v1 = 0.f;
-      for (int r = 0; r < npart; ++r) {
-        if (EPI == EPI_SILU) {
-          v0 += *cluster.map_shared_rank(cta_part + idx, 2 * r);        // w1 partials (x index 0)
-          v1 += *cluster.map_shared_rank(cta_part + idx, 2 * r + 1);    // w3 partials
-        } else {
-          v0 += *cluster.map_shared_rank(cta_part + idx, r);
+      if (EPI == EPI_SILU) {
+        float t0[8], t1[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          t0[r] = (r < npart) ? *cluster.map_shared_rank(cta_part + idx, 2 * r) : 0.f;       // w1 partials
+          t1[r] = (r < npart) ? *cluster.map_shared_rank(cta_part + idx, 2 * r + 1) : 0.f;   // w3 partials
         }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) { v0 += t0[r]; v1 += t1[r]; }
+      } else {
+        float t0[16];
+#pragma unroll
+        for (int r = 0; r < 16; ++r) t0[r] = (r < npart) ? *cluster.map_shared_rank(cta_part + idx, r) : 0.f;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) v0 += t0[r];
       }
       const int n = f_span_col(span, lc);
       if (n < pr.N) {
@@ -319,7 +343,7 @@ template <int MT, int PRO, int EPI>
 static int launch_fused(const FusedParams& p, int grid_x, int nsplit, int cluster_x, cudaStream_t st, bool pdl) {
   auto kern = gemv_fused_kernel<MT, PRO, EPI>;
   const size_t ring = (size_t)FW * F_DEPTH * F_SLOT_BYTES;
-  const size_t xs = (size_t)MT * 8 * (p.rows_per_split + F_XS_PAD) * 2 + 64;
+  const size_t xs = (size_t)MT * 8 * (p.rows_per_split + F_XS_PAD) * 2 + 64 + (size_t)p.rows_per_split * 2;
   const size_t red = (size_t)FW * MT * 16 * 32 * 16 + (size_t)p.M * F_SPAN_COLS * 4;
   const size_t smem = (ring + xs) > red ? (ring + xs) : red;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
