@@ -78,6 +78,19 @@ int q40_gemm_kn(const void* a, int64_t lda, const void* bw, const void* bs, void
                 int64_t ldc, int M, int N, int K, int group, void* workspace,
                 size_t workspace_bytes, void* stream);
 
+/* q40_gemm_kn without a caller-provided workspace, for hosts that cannot allocate device
+ * memory themselves (all HBM already handed to their own planner, or a plug-in that only
+ * receives input and output buffers).  The split-K scratch is a fixed array inside the library
+ * (q40_gemm_kn_static_max_workspace() bytes, 8 MiB, held on every GPU that loads the library);
+ * a problem whose q40_gemm_workspace_bytes() exceeds it returns Q40_E_WORKSPACE.  The first
+ * call on a device looks up the array's device address and should precede any stream
+ * capture.  Calls share the array, so calls that overlap on the GPU race; calls on one
+ * stream are safe.  No allocation is made by this entry point or anything it calls.
+ * This entry point has no counterpart in the reference. */
+int q40_gemm_kn_static(const void* a, int64_t lda, const void* bw, const void* bs, void* c,
+                       int64_t ldc, int M, int N, int K, int group, void* stream);
+size_t q40_gemm_kn_static_max_workspace(void);
+
 /* Y[M,N] = X[M,K] @ deq(W)[N,K]^T, W quantised from a row-major [N,K] matrix (groups
  * along K): wq viewed as [N*K/(2*group), group], ws as [N*K/group].  K % (2*group) == 0.
  * Replaces: dequantize_q40 + F.linear in LinearQ4_0.forward (quantize.py:235-246,

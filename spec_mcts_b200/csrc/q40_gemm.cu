@@ -603,3 +603,53 @@ extern "C" int q40_gemm_nk(const void* x, int64_t ldx, const void* wq, const voi
   }
   return Q40_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// q40_gemm_kn_static: q40_gemm_kn for callers that cannot hand over a workspace.
+//
+// Some hosts of this library own no allocator of their own on the device: a serving process
+// that handed every byte of HBM to its memory planner at start-up, or a plug-in that is only
+// given input and output buffers by the runtime that loads it.  For them the split-K scratch
+// lives inside the library, in the fixed-size device array below.  Every GPU that loads the
+// library carries these Q40_STATIC_WS_BYTES until the process exits; problems whose scratch
+// need is larger are refused with Q40_E_WORKSPACE (use q40_gemm_kn with your own buffer).
+//
+// The array's name is only a handle on the host side; the kernels need its device address,
+// which is looked up once per device (cudaGetSymbolAddress, with that device current) by the
+// first call made on that device.  That first call also does nothing else unusual, but
+// because it performs this look-up it should be made before any stream capture is begun.
+// All calls share the one array: the arrival counters at its start are cleared on the
+// stream before every launch, the partial sums behind them are fully overwritten before
+// they are read, and two calls that overlap on the GPU (different streams) would race.
+// Nothing here calls cudaMalloc, cudaFree or any allocating library routine.
+// ---------------------------------------------------------------------------------------
+#define Q40_STATIC_WS_BYTES (8u * 1024u * 1024u)
+
+static __device__ __align__(256) unsigned char q40_static_ws[Q40_STATIC_WS_BYTES];
+
+static void* q40_static_ws_ptr[64];       // device address of the array, per device ordinal
+static bool q40_static_ws_ready[64];
+
+extern "C" size_t q40_gemm_kn_static_max_workspace(void) { return (size_t)Q40_STATIC_WS_BYTES; }
+
+extern "C" int q40_gemm_kn_static(const void* a, int64_t lda, const void* bw, const void* bs, void* c,
+                                  int64_t ldc, int M, int N, int K, int group, void* stream) {
+  if (M > 0 && N > 0 && K > 0 && q40_gemm_workspace_bytes(M, N, K) > (size_t)Q40_STATIC_WS_BYTES)
+    return Q40_E_WORKSPACE;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return Q40_E_UNSUPPORTED;
+  if (!q40_static_ws_ready[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, q40_static_ws);
+    if (e != cudaSuccess) return (int)e;
+    q40_static_ws_ptr[dev] = ptr;
+    q40_static_ws_ready[dev] = true;
+  }
+  void* ws = q40_static_ws_ptr[dev];
+  // the counters must read zero when a launch starts, whatever an earlier call left behind
+  e = cudaMemsetAsync(ws, 0, q40::COUNTER_BYTES, (cudaStream_t)stream);
+  if (e != cudaSuccess) return (int)e;
+  return q40_gemm_kn(a, lda, bw, bs, c, ldc, M, N, K, group, ws, (size_t)Q40_STATIC_WS_BYTES, stream);
+}
