@@ -236,39 +236,123 @@ def timed_e2e(model, width, steps, warmup, prompt_len):
 
 
 def gemv_roofline(model, width, reps):
-    """The dominant kernel alone: every Q4_0 linear of the model in layer order (3.4 GB of
-    distinct weights per pass, so nothing is served from L2), CUDA events around the passes."""
+    """The dominant kernel alone: every Q4_0 matmul of the model in layer order (3.4 GB of
+    distinct weights per pass, so nothing is served from L2), launched exactly as a decode step
+    launches them (for width <= 16 the cluster-reduced kernel, [wq,wk,wv] and [w1,w3] sharing a
+    launch) but with nothing in between, replayed from a CUDA graph so that the host does not
+    pace the launches; CUDA events around the replays on the replaying stream."""
     import torch
+    from spec_mcts_b200 import kernels as K
     from spec_mcts_b200._lib import check, lib
     dev = model.device
-    st = torch.cuda.current_stream(dev).cuda_stream
-    lins = []
+    fused = model.use_fused and width <= 16
+    groups = []
     for layer in model.layers:
         a, f = layer.attention, layer.feed_forward
-        lins += [a.wq, a.wk, a.wv, a.wo, f.w1, f.w3, f.w2]
+        groups += [[a.wq, a.wk, a.wv], [a.wo], [f.w1, f.w3], [f.w2]] if fused else \
+            [[a.wq], [a.wk], [a.wv], [a.wo], [f.w1], [f.w3], [f.w2]]
     xs = {k: torch.randn((width, k), device=dev, dtype=torch.float16) for k in (DIM, FFN)}
-    outs = {n: torch.empty((width, n), device=dev, dtype=torch.float16) for n in (DIM, FFN)}
+    out = torch.empty((width, 3 * FFN), device=dev, dtype=torch.float16)
     ws = torch.zeros(max(lib.q40_gemm_workspace_bytes(width, n, k) for n, k in LAYER_SHAPES), dtype=torch.uint8,
                      device=dev)
 
     def one_pass():
-        for lin in lins:
-            k, n = lin.kn()
-            check(lib.q40_gemm_kn(xs[k].data_ptr(), k, lin.w.data_ptr(), lin.s.data_ptr(), outs[n].data_ptr(), n,
-                                  width, n, k, 64, ws.data_ptr(), ws.numel(), st))
-    for _ in range(3):
+        st = torch.cuda.current_stream(dev).cuda_stream
+        for grp in groups:
+            k, n = grp[0].kn()
+            if fused:
+                W = n * len(grp)
+                outs = [out[:, i * n:(i + 1) * n] for i in range(len(grp))]
+                model._fused(0, grp, outs, 3 * FFN, xs[k], k, width, st=st)
+            else:
+                check(lib.q40_gemm_kn(xs[k].data_ptr(), k, grp[0].w.data_ptr(), grp[0].s.data_ptr(), out.data_ptr(),
+                                      3 * FFN, width, n, k, 64, ws.data_ptr(), ws.numel(), st))
+
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
         one_pass()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    torch.cuda.synchronize(dev)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        one_pass()
+    for _ in range(3):
+        g.replay()
     torch.cuda.synchronize(dev)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(reps):
-        one_pass()
+        g.replay()
     e1.record()
     torch.cuda.synchronize(dev)
     sec = e0.elapsed_time(e1) * 1e-3
-    launches = reps * len(lins) * ((width + 15) // 16)
-    total_bytes = reps * sum(q4_bytes(lin.kn()[1], lin.kn()[0], width) for lin in lins)
-    return total_bytes / sec / 1e9, sec / launches, total_bytes / launches
+    passes = (width + 15) // 16 if not fused else 1
+    launches = reps * len(groups) * passes
+    total_bytes = reps * sum(q4_bytes(l.kn()[1], l.kn()[0], width) for grp in groups for l in grp)
+    name = "gemv_fused_kernel<%d,0,0>" % (1 if width <= 8 else 2) if fused else "gemv_kn_kernel<64,%d>" % (1 if width <= 8 else 2)
+    return total_bytes / sec / 1e9, sec / launches, total_bytes / launches, name
+
+
+def run_70b_tp(args):
+    """`--workload 70b-tp` (launch with torchrun, one rank per GPU): CodeLlama-70B-architecture
+    Q4_0 decode, 80 layers, hidden 8192, 64 query / 8 kv heads, FFN 28672, vocab 32016, random
+    shards per rank, prompt cache of 1024 tokens, 64 branches; tensor parallel over all ranks
+    with an NCCL all-reduce after wo and w2.  Prints its own JSON line on rank 0."""
+    import torch
+    import torch.distributed as dist
+    from spec_mcts_b200.model import ModelArgs, Transformer, random_init_
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, P, steps, warmup = args.tp_branches, 1024, args.steps, max(args.warmup, 3)
+    margs = ModelArgs(dim=8192, n_layers=args.tp_layers, n_heads=64, n_kv_heads=8, vocab_size=VOCAB, multiple_of=4096,
+                      ffn_dim_multiplier=1.3, max_batch_size=B, max_seq_len=max(steps + warmup + 2, 72),
+                      max_prompt_seq_len=P)
+    with torch.inference_mode():
+        model = Transformer(margs, device=dev, tp_rank=rank, tp_world=world)
+        random_init_(model, seed=1000 + rank)
+        model = model.to(dev, torch.float16)
+        model._caches["pk"].normal_()
+        model._caches["pv"].normal_()
+        model._prefix_len_dev.fill_(P)
+        torch.cuda.synchronize(dev)
+        model.greedy_feedback = True
+        model._pos_dev[:B].fill_(P)
+        model._tok_dev[:B].copy_(torch.arange(B, device=dev) % VOCAB)
+        for _ in range(warmup):
+            model.decode_replay(B)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            model.decode_replay(B)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        sec = e0.elapsed_time(e1) * 1e-3
+        if world > 1:
+            t = torch.tensor([sec], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            sec = float(t.item())
+    if rank == 0:
+        hid = model.layers[0].feed_forward.full_hidden_dim
+        per_layer = (8192 * 8192 * 2 + 2 * 8192 * 1024 + 3 * 8192 * hid)
+        wbytes = margs.n_layers * (per_layer // 2 + per_layer // 64 * 2) / world + VOCAB * 8192 * 2
+        print(json.dumps({"workload": "codellama-70b-arch q4_0 decode, tensor parallel", "n_gpus": world,
+                          "layers": margs.n_layers, "branches": B, "prompt_len": P, "steps": steps,
+                          "ms_per_step": sec / steps * 1e3, "tokens_per_s": B * steps / sec,
+                          "weight_bytes_per_gpu_per_step": wbytes,
+                          "weight_stream_gbs_per_gpu": wbytes / (sec / steps) / 1e9,
+                          "allreduces_per_step": 2 * margs.n_layers, "allreduce_bytes": B * 8192 * 2}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def main():
@@ -282,7 +366,13 @@ def main():
     ap.add_argument("--skip-prefill", action="store_true",
                     help="profiling aid: fill the prompt cache with random K/V instead of running the prompt "
                          "(keeps a profiler capture short); not a valid benchmark configuration")
+    ap.add_argument("--workload", default="7b", choices=["7b", "70b-tp"])
+    ap.add_argument("--tp-layers", type=int, default=80)
+    ap.add_argument("--tp-branches", type=int, default=64)
     args = ap.parse_args()
+    if args.workload == "70b-tp" and args.impl != "reference":
+        run_70b_tp(args)
+        return
     if args.impl == "reference":
         run_reference_arm(args)
         return
@@ -356,7 +446,7 @@ def main():
         w0 = widths[0]
         tok_s = {w: world * w * steps / results[w] for w in widths}
         e2e_tok_s = {w: world * w * steps / e2e_res[w][0] for w in widths}
-        ach, sec_per_launch, bytes_per_launch = roof
+        ach, sec_per_launch, bytes_per_launch, roof_kernel = roof
         step_bytes = step_weight_bytes()
         line = {
             "metric": METRIC, "value": tok_s[w0], "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
@@ -372,7 +462,7 @@ def main():
             "step_weight_stream": {"bytes_per_step": step_bytes,
                                    "achieved_gbs": step_bytes / (results[w0] / steps) / 1e9,
                                    "frac_of_%s_hbm" % peak_kind: step_bytes / (results[w0] / steps) / 1e9 / hbm_peak},
-            "roofline": {"bound": "hbm", "kernel": "gemv_kn_kernel<64,1>", "achieved": ach, "peak": hbm_peak,
+            "roofline": {"bound": "hbm", "kernel": roof_kernel, "achieved": ach, "peak": hbm_peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": ach / hbm_peak,
                          "avg_launch_us": sec_per_launch * 1e6, "alg_bytes_per_launch": bytes_per_launch,
                          "traffic": None},

@@ -94,19 +94,22 @@ class LinearQ4_0(nn.Module):
 
 
 class Attention(nn.Module):
-    def __init__(self, args: ModelArgs, layer_id: int, caches):
+    def __init__(self, args: ModelArgs, layer_id: int, caches, tp_world: int = 1):
         super().__init__()
         self.args = args
         self.n_kv_heads = args.n_heads if args.n_kv_heads is None else args.n_kv_heads
         assert args.n_heads % self.n_kv_heads == 0
-        self.n_local_heads = args.n_heads
-        self.n_local_kv_heads = self.n_kv_heads
+        # tensor parallel: query heads and kv heads are split across ranks (the reference fixes
+        # model_parallel_size = 1, hf_model_q40_kv_shared.py:258-260)
+        assert args.n_heads % tp_world == 0 and self.n_kv_heads % tp_world == 0
+        self.n_local_heads = args.n_heads // tp_world
+        self.n_local_kv_heads = self.n_kv_heads // tp_world
         self.n_rep = self.n_local_heads // self.n_local_kv_heads
         self.head_dim = args.dim // args.n_heads
-        self.wq = LinearQ4_0(args.dim, args.n_heads * self.head_dim, GROUP_SIZE)
-        self.wk = LinearQ4_0(args.dim, self.n_kv_heads * self.head_dim, GROUP_SIZE)
-        self.wv = LinearQ4_0(args.dim, self.n_kv_heads * self.head_dim, GROUP_SIZE)
-        self.wo = LinearQ4_0(args.n_heads * self.head_dim, args.dim, GROUP_SIZE)
+        self.wq = LinearQ4_0(args.dim, self.n_local_heads * self.head_dim, GROUP_SIZE)
+        self.wk = LinearQ4_0(args.dim, self.n_local_kv_heads * self.head_dim, GROUP_SIZE)
+        self.wv = LinearQ4_0(args.dim, self.n_local_kv_heads * self.head_dim, GROUP_SIZE)
+        self.wo = LinearQ4_0(self.n_local_heads * self.head_dim, args.dim, GROUP_SIZE)
         # views into the model-wide cache tensors (same names as the reference's attributes)
         self.cache_prompt_k = caches["pk"][layer_id]     # [maxP, Hkv, D] fp16
         self.cache_prompt_v = caches["pv"][layer_id]
@@ -118,12 +121,16 @@ class Attention(nn.Module):
 
 
 class FeedForward(nn.Module):
-    def __init__(self, dim: int, hidden_dim: int, multiple_of: int, ffn_dim_multiplier: Optional[float]):
+    def __init__(self, dim: int, hidden_dim: int, multiple_of: int, ffn_dim_multiplier: Optional[float],
+                 tp_world: int = 1):
         super().__init__()
         hidden_dim = int(2 * hidden_dim / 3)
         if ffn_dim_multiplier is not None:
             hidden_dim = int(ffn_dim_multiplier * hidden_dim)
         hidden_dim = multiple_of * ((hidden_dim + multiple_of - 1) // multiple_of)
+        self.full_hidden_dim = hidden_dim
+        assert hidden_dim % (128 * tp_world) == 0, "the FFN width must split into 128-column blocks per rank"
+        hidden_dim //= tp_world          # this rank's columns of w1/w3 and rows of w2
         self.hidden_dim = hidden_dim
         self.w1 = LinearQ4_0(dim, hidden_dim, GROUP_SIZE)
         self.w2 = LinearQ4_0(hidden_dim, dim, GROUP_SIZE)
@@ -134,14 +141,14 @@ class FeedForward(nn.Module):
 
 
 class TransformerBlock(nn.Module):
-    def __init__(self, layer_id: int, args: ModelArgs, caches):
+    def __init__(self, layer_id: int, args: ModelArgs, caches, tp_world: int = 1):
         super().__init__()
         self.n_heads = args.n_heads
         self.dim = args.dim
         self.head_dim = args.dim // args.n_heads
-        self.attention = Attention(args, layer_id, caches)
+        self.attention = Attention(args, layer_id, caches, tp_world)
         self.feed_forward = FeedForward(dim=args.dim, hidden_dim=4 * args.dim, multiple_of=args.multiple_of,
-                                        ffn_dim_multiplier=args.ffn_dim_multiplier)
+                                        ffn_dim_multiplier=args.ffn_dim_multiplier, tp_world=tp_world)
         self.layer_id = layer_id
         self.attention_norm = RMSNorm(args.dim, eps=args.norm_eps)
         self.ffn_norm = RMSNorm(args.dim, eps=args.norm_eps)
@@ -152,8 +159,13 @@ class Transformer(nn.Module):
     prompt cache), start_pos > 0 with one token per branch is a decode step
     (hf_model_q40_kv_shared.py:492-510)."""
 
-    def __init__(self, params: ModelArgs, device: Optional[torch.device] = None):
+    def __init__(self, params: ModelArgs, device: Optional[torch.device] = None, tp_rank: int = 0,
+                 tp_world: int = 1, process_group=None):
+        """tp_world > 1: Megatron-style tensor parallelism over one process per GPU — wq/wk/wv/w1/w3
+        hold this rank's output columns, wo/w2 its input rows, and the partial outputs of wo and w2
+        are summed with an all-reduce over `process_group` (NCCL)."""
         super().__init__()
+        self.tp_rank, self.tp_world, self.tp_group = tp_rank, tp_world, process_group
         if not torch.cuda.is_available():
             raise RuntimeError("spec_mcts_b200.model needs a CUDA device (no CPU path)")
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
@@ -161,9 +173,10 @@ class Transformer(nn.Module):
         self.vocab_size = params.vocab_size
         self.n_layers = params.n_layers
         p = params
-        Hkv = p.n_heads if p.n_kv_heads is None else p.n_kv_heads
+        Hkv = (p.n_heads if p.n_kv_heads is None else p.n_kv_heads) // tp_world    # local kv heads
         D = p.dim // p.n_heads
         assert D == 128, "the attention kernels are written for head_dim 128"
+        self._H = p.n_heads // tp_world                                            # local query heads
         L, dev = p.n_layers, self.device
         self._caches = {
             "pk": torch.zeros((L, p.max_prompt_seq_len, Hkv, D), dtype=DTYPE, device=dev),
@@ -174,7 +187,7 @@ class Transformer(nn.Module):
             "vs": torch.zeros((L, p.max_batch_size, p.max_seq_len, Hkv, 2), dtype=DTYPE, device=dev),
         }
         self.tok_embeddings = nn.Embedding(p.vocab_size, p.dim, device="meta")
-        self.layers = nn.ModuleList(TransformerBlock(i, p, self._caches) for i in range(p.n_layers))
+        self.layers = nn.ModuleList(TransformerBlock(i, p, self._caches, tp_world) for i in range(p.n_layers))
         self.norm = RMSNorm(p.dim, eps=p.norm_eps)
         self.output = nn.Linear(p.dim, p.vocab_size, bias=False, device="meta")
         self.freqs_cis = precompute_freqs_cis(D, p.max_seq_len + p.max_prompt_seq_len, p.rope_theta)
@@ -229,7 +242,7 @@ class Transformer(nn.Module):
         assert bsz == 1, "the prompt is processed once and shared by all branches"
         assert S <= p.max_prompt_seq_len
         dev = self.device
-        H, Hkv, D = p.n_heads, self._Hkv, self._D
+        H, Hkv, D = self._H, self._Hkv, self._D
         h = self.tok_embeddings(tokens.to(dev)).to(DTYPE).view(S, p.dim)
         pos = torch.arange(S, dtype=torch.int32, device=dev)
         for li, layer in enumerate(self.layers):
@@ -252,11 +265,11 @@ class Transformer(nn.Module):
                 v_ = v_.repeat_interleave(H // Hkv, dim=1)
             o = F.scaled_dot_product_attention(q_, k_, v_, is_causal=True)
             o = o[0].transpose(0, 1).reshape(S, H * D)
-            ao = K.matmul_q40(o.contiguous(), att.wo.w, att.wo.s, att.wo.kn())
+            ao = self._all_reduce(K.matmul_q40(o.contiguous(), att.wo.w, att.wo.s, att.wo.kn()))
             hn, h = K.rmsnorm(h, layer.ffn_norm.weight, p.norm_eps, residual=ao)
             a1 = K.matmul_q40(hn, ff.w1.w, ff.w1.s, ff.w1.kn())
             a3 = K.matmul_q40(hn, ff.w3.w, ff.w3.s, ff.w3.kn())
-            f2 = K.matmul_q40(K.silu_mul(a1, a3), ff.w2.w, ff.w2.s, ff.w2.kn())
+            f2 = self._all_reduce(K.matmul_q40(K.silu_mul(a1, a3), ff.w2.w, ff.w2.s, ff.w2.kn()))
             h = h + f2
         self._prefix_len_dev.fill_(S)
         hn = K.rmsnorm(h, self.norm.weight, p.norm_eps)
@@ -267,7 +280,7 @@ class Transformer(nn.Module):
         b = self._bufs.get(B)
         if b is None:
             p, dev = self.params, self.device
-            H, Hkv, D = p.n_heads, self._Hkv, self._D
+            H, Hkv, D = self._H, self._Hkv, self._D
             hid = self.layers[0].feed_forward.hidden_dim
             e = lambda *s: torch.empty(s, dtype=DTYPE, device=dev)
             nb_attn = lib.q40_attn_shared_prefix_workspace_bytes(B, H, D, p.max_prompt_seq_len)
@@ -292,7 +305,7 @@ class Transformer(nn.Module):
 
     def _decode_body(self, B):
         """Enqueue one decode step for B branches on the current stream (captured into a graph)."""
-        if self.use_fused and B <= 16:
+        if self.use_fused and B <= 16 and self.tp_world == 1:
             return self._decode_body_fused(B)
         return self._decode_body_unfused(B)
 
@@ -318,7 +331,7 @@ class Transformer(nn.Module):
         rope+append, 2 attention, wo with residual epilogue, w1/w3 with RMSNorm prologue and
         SiLU-mul epilogue, w2 with residual epilogue), chained with programmatic dependent launch."""
         p, bufs = self.params, self._step_buffers(B)
-        H, Hkv, D = p.n_heads, self._Hkv, self._D
+        H, Hkv, D = self._H, self._Hkv, self._D
         self._check_loaded()
         st = torch.cuda.current_stream(self.device).cuda_stream
         hid = self.layers[0].feed_forward.hidden_dim
@@ -363,7 +376,7 @@ class Transformer(nn.Module):
     def _decode_body_unfused(self, B):
         """One launch per operation; serves any batch width."""
         p, bufs = self.params, self._step_buffers(B)
-        H, Hkv, D = p.n_heads, self._Hkv, self._D
+        H, Hkv, D = self._H, self._Hkv, self._D
         self._check_loaded()
         st = torch.cuda.current_stream(self.device).cuda_stream
         h, xn = bufs["h"], bufs["xn"]
@@ -392,12 +405,14 @@ class Transformer(nn.Module):
                                            bufs["ao"].data_ptr(), B, H, Hkv, D, aws.data_ptr(), aws.numel(), st),
                   "q40_attn_tree_decode")
             self._gemm(bufs, bufs["ao"], att.wo, bufs["o"], st)
+            self._all_reduce(bufs["o"])
             self._norm(h, bufs["o"], layer.ffn_norm.weight, xn, st)
             self._gemm(bufs, xn, ff.w1, bufs["a1"], st)
             self._gemm(bufs, xn, ff.w3, bufs["a3"], st)
             check(lib.q40_silu_mul(bufs["a1"].data_ptr(), bufs["a3"].data_ptr(), bufs["g"].data_ptr(),
                                    bufs["g"].numel(), st), "q40_silu_mul")
             self._gemm(bufs, bufs["g"], ff.w2, bufs["f"], st)
+            self._all_reduce(bufs["f"])
             pending = bufs["f"]
         self._norm(h, pending, self.norm.weight, xn, st)
         torch.matmul(xn, self.output.weight.t(), out=bufs["logits"])
@@ -405,6 +420,13 @@ class Transformer(nn.Module):
             self._tok_dev[:B].copy_(bufs["logits"].argmax(dim=-1))
             self._pos_dev[:B] += 1
         return bufs["logits"]
+
+    def _all_reduce(self, t):
+        """Sum the partial outputs of a row-parallel matmul over the tensor-parallel ranks."""
+        if self.tp_world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.tp_group)
+        return t
 
     def _check_loaded(self):
         for t in (self.norm.weight, self.layers[0].attention_norm.weight, self.output.weight,
@@ -431,7 +453,7 @@ class Transformer(nn.Module):
     def decode_replay(self, B):
         """Run one decode step for B branches with the tokens/positions already in the device
         buffers (`_tok_dev`, `_pos_dev`); returns the static logits buffer [B, vocab]."""
-        fused = self.use_fused and B <= 16
+        fused = self.use_fused and B <= 16 and self.tp_world == 1
         self.launches_per_step = self.params.n_layers * (7 if fused else 13) + (2 if fused else 1)
         if not self.use_cuda_graph:
             return self._decode_body(B)
@@ -480,7 +502,7 @@ def random_init_(model: Transformer, seed: int = 0, std: float = 0.02) -> None:
 
     for layer in model.layers:
         att, ff = layer.attention, layer.feed_forward
-        H, Hkv, D = p.n_heads, model._Hkv, model._D
+        H, Hkv, D = model._H, model._Hkv, model._D
         fill(att.wq, p.dim, H * D)
         fill(att.wk, p.dim, Hkv * D)
         fill(att.wv, p.dim, Hkv * D)
