@@ -78,6 +78,16 @@ int q40_gemm_kn(const void* a, int64_t lda, const void* bw, const void* bs, void
                 int64_t ldc, int M, int N, int K, int group, void* workspace,
                 size_t workspace_bytes, void* stream);
 
+/* The tensor-core form q40_gemm_kn selects for M > 16 (group 64, K % 64 == 0, N % 128 == 0):
+ * tcgen05.mma with the 128 output features of a packed block as the MMA M dimension and the
+ * batch as N, accumulator in tensor memory, split-K over a thread-block cluster.  `err` is a
+ * device int (zeroed by the caller) that the kernel sets to 1 if one of its bounded waits
+ * expired, in which case the output is undefined; through q40_gemm_kn it is the last int of the
+ * first 4096 bytes of the workspace.
+ * Replaces: matmul_q40 (triton_kernels.py:357-500) at batch 100 and for the prompt pass. */
+int q40_gemm_kn_tc(const void* a, int64_t lda, const void* bw, const void* bs, void* c, int64_t ldc,
+                   int M, int N, int K, int* err, void* stream);
+
 /* q40_gemm_kn without a caller-provided workspace, for hosts that cannot allocate device
  * memory themselves (all HBM already handed to their own planner, or a plug-in that only
  * receives input and output buffers).  The split-K scratch is a fixed array inside the library

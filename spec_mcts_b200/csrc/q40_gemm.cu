@@ -474,6 +474,9 @@ static NkPlan plan_nk(int N, int K) {
 
 }  // namespace q40
 
+extern "C" int q40_gemm_kn_tc(const void* a, int64_t lda, const void* bw, const void* bs, void* c, int64_t ldc,
+                              int M, int N, int K, int* err, void* stream);
+
 extern "C" size_t q40_gemm_workspace_bytes(int M, int N, int K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const q40::GemvPlan p = q40::plan_kn(N, K);
@@ -523,8 +526,13 @@ extern "C" int q40_gemm_kn(const void* a, int64_t lda, const void* bw, const voi
   cudaStream_t st = (cudaStream_t)stream;
   const __half* ah = (const __half*)a;
   __half* ch = (__half*)c;
-  // batches above 16 rows are processed 16 rows at a time (the weights of the decode
-  // shapes stay L2-resident between passes)
+  // batches above 16 rows go to the tcgen05 kernel when the shape allows it; its error word is the
+  // last int of the (zeroed) counter header of the workspace
+  if (M > 16 && group == 64 && K % 64 == 0 && workspace && workspace_bytes >= (size_t)q40::COUNTER_BYTES &&
+      p.nspans * 4 <= q40::COUNTER_BYTES - 4)
+    return q40_gemm_kn_tc(a, lda, bw, bs, c, ldc, M, N, K,
+                          reinterpret_cast<int*>((char*)workspace + q40::COUNTER_BYTES - 4), stream);
+  // otherwise batches above 16 rows are processed 16 rows at a time
   for (int m0 = 0; m0 < M; m0 += 16) {
     const int mc = (M - m0) < 16 ? (M - m0) : 16;
     int rc;

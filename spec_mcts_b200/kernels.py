@@ -22,7 +22,7 @@ __all__ = [
     "quantize_q40", "dequantize_q40", "triton_deq_int40", "triton_q_int40", "triton_q_int40_sliced",
     "quantize_q40_rows", "matmul", "matmul_q40", "linear_q40", "flash_attn", "page_flash_attn",
     "triton_attn", "chunk_attn", "shared_prefix_attn", "matmul_split_k", "rmsnorm", "rope_", "silu_mul",
-    "gemv_fused", "embed_rows",
+    "gemv_fused", "embed_rows", "tc_error_flag",
     "Q40Error",
 ]
 
@@ -175,6 +175,16 @@ def matmul_q40(a: torch.Tensor, b_w: torch.Tensor, b_s: torch.Tensor, b_shape, *
                           c.stride(0), M, N, K, group_size, ws.data_ptr(), ws.numel(), _stream(dev)),
           "q40_gemm_kn")
     return c
+
+
+def tc_error_flag(dev=None) -> int:
+    """1 if a tensor-core matmul launched through matmul_q40 on the current stream of `dev` gave up
+    on one of its bounded waits since the workspace was created (synchronises the device)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if dev is None else dev
+    buf = _workspaces.get(("gemm", dev.index, _stream(dev)))
+    if buf is None:
+        return 0
+    return int(buf[4092:4096].view(torch.int32).item())
 
 
 def linear_q40(x: torch.Tensor, w_q: torch.Tensor, w_s: torch.Tensor, w_shape, *,

@@ -138,7 +138,7 @@ def _rand_q(rng, rows, cols, G, std=0.02):
     return q, s
 
 
-@pytest.mark.parametrize("M", [1, 2, 8, 9, 16, 17, 33, 100])
+@pytest.mark.parametrize("M", [1, 2, 8, 9, 16, 17, 33, 100, 130, 256, 300])
 @pytest.mark.parametrize("KN", [(128, 128), (256, 384), (1024, 1152), (712, 256), (2048, 4096)])
 @pytest.mark.parametrize("G", [64, 32])
 def test_matmul_kn_vs_oracle(K, M, KN, G):
@@ -151,6 +151,7 @@ def test_matmul_kn_vs_oracle(K, M, KN, G):
     c = K.matmul_q40(dev(a), dev(q), dev(s), (Kd, N), group_size=G)
     assert tuple(c.shape) == (M, N) and c.dtype == torch.float16
     assert_close(host(c), O.matmul_q40(a, q, s, (Kd, N), G))
+    assert K.tc_error_flag() == 0     # no bounded wait of the tensor-core kernel expired
 
 
 @pytest.mark.parametrize("M", [1, 7, 16, 40])
