@@ -351,8 +351,11 @@ def run_70b_tp(args):
                           "weight_stream_gbs_per_gpu": wbytes / (sec / steps) / 1e9,
                           "allreduces_per_step": 2 * margs.n_layers, "allreduce_bytes": B * 8192 * 2}), flush=True)
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        # captured graphs hold NCCL work; tearing the process group down under them can block, and
+        # there is nothing left to save: synchronise and leave
+        torch.cuda.synchronize(dev)
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def main():
@@ -482,8 +485,11 @@ def main():
             line["cpu_baseline"] = None
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        # captured graphs hold NCCL work; tearing the process group down under them can block, and
+        # there is nothing left to save: synchronise and leave
+        torch.cuda.synchronize(dev)
+        sys.stdout.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

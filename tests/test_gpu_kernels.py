@@ -187,7 +187,10 @@ def test_matmul_7b_shapes_linearity_and_repeatability(K):
         assert torch.equal(c100, K.matmul_q40(x, q, s, (Kd, N)))
         c1 = K.matmul_q40(x[37:38].contiguous(), q, s, (Kd, N))
         c10 = K.matmul_q40(x[30:40].contiguous(), q, s, (Kd, N))
-        assert torch.equal(c1[0], c100[37]) and torch.equal(c10[7], c100[37])
+        # rows do not depend on their batch within a kernel family (M <= 16: split-K GEMV); the
+        # tensor-core kernel used above 16 rows sums in a different order, so it is compared closely
+        assert torch.equal(c1[0], c10[7])
+        assert_close(host(c100[37:38]), host(c1), rtol=1e-2, atol=2e-3)
         ref = (x[:4].float() @ deq.float()).to(torch.float16)
         assert_close(host(c100[:4]), host(ref))
 
