@@ -134,6 +134,27 @@ int q40_gemv_fused(int mode, int nmat, const void* const* bw, const void* const*
                    void* stream);
 int q40_gemv_fused_ss_count(int N, int K, int max_cluster);
 
+/* One whole decode step of the KV-shared Q4_0 model for 1 <= M <= 8 branches as a single
+ * persistent launch: embedding, every layer ([wq,wk,wv] with RMSNorm, rotary embedding + Q4_0
+ * cache append + attention over shared prompt / packed suffix / new token, wo + residual,
+ * [w1,w3] with RMSNorm and SiLU-mul, w2 + residual) and the final RMSNorm, which is left in `xn`
+ * [M, dim] for the caller's lm_head.  `layers` is a device array of n_layers records of 22
+ * device pointers: packed weights wq wk wv wo w1 w3 w2, their scales in the same order,
+ * attention_norm, ffn_norm, prompt K, prompt V ([max_p, Hkv, 128] fp16), suffix K bytes, K scales,
+ * V bytes, V scales ([maxB, max_t, Hkv, 64] / [.., 2]).  tokens int64 [M], pos int32 [M] (absolute
+ * positions), prefix_len int32 [1], cos/sin fp16 [n_pos, 64].  h/qkv/ao/g/xn, ss_a/ss_f
+ * ([M, 1024] floats), bar and err are caller-owned device scratch; bar and err are zeroed on the
+ * stream by this call; *err != 0 afterwards means a bounded wait between CTAs expired and the
+ * result is undefined.  max_cluster 16 or 8.  Needs an otherwise idle GPU (all CTAs must be
+ * resident at once).
+ * Replaces: Transformer.forward for one decode step (hf_model_q40_kv_shared.py:492-510). */
+int q40_decode_step(const void* layers, int n_layers, int M, int dim, int H, int Hkv, int hidden,
+                    int vocab, int max_t, int max_p, int n_pos, float eps, const void* emb,
+                    const void* final_norm, const int64_t* tokens, const int32_t* pos,
+                    const int32_t* prefix_len, const void* cos_tbl, const void* sin_tbl, void* h,
+                    void* qkv, void* ao, void* g, void* xn, float* ss_a, float* ss_f,
+                    unsigned int* bar, int* err, int max_cluster, void* stream);
+
 /* ---- decode attention (one query token per branch) ---------------------------------- */
 
 /* q[B,H,D], k/v[B,Hkv,L,D] contiguous fp16 -> o[B,H,D]; scale 1/sqrt(D); D == 128;

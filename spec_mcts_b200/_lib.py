@@ -53,6 +53,10 @@ SIGNATURES = {
                                c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int64, c_void_p,
                                c_int, c_int, c_int, c_void_p]),
     "q40_gemv_fused_ss_count": (c_int, [c_int, c_int, c_int]),
+    "q40_decode_step": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_int, c_void_p]),
     "q40_attn_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p]),
     "q40_attn_paged": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,

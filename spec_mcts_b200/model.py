@@ -211,6 +211,9 @@ class Transformer(nn.Module):
         self.use_fused = True
         self.use_pdl = True
         self.max_cluster = 16
+        # B <= 8 without tensor parallelism can run the whole step as one persistent kernel
+        self.use_megakernel = True
+        self._layer_table = None
 
     # ------------------------------------------------------------------ reference API
     @torch.inference_mode()
@@ -291,6 +294,7 @@ class Transformer(nn.Module):
                      attn_ws=torch.empty(nb_attn, dtype=torch.uint8, device=dev),
                      gemm_ws=torch.zeros(nb_gemm, dtype=torch.uint8, device=dev),
                      logits=e(B, p.vocab_size), qkv=e(B, (H + 2 * Hkv) * D),
+                     sync=torch.zeros(2, dtype=torch.int32, device=dev),
                      ss_attn=torch.zeros((B, 1024), dtype=torch.float32, device=dev),
                      ss_ffn=torch.zeros((B, 1024), dtype=torch.float32, device=dev))
             self._bufs[B] = b
@@ -305,6 +309,8 @@ class Transformer(nn.Module):
 
     def _decode_body(self, B):
         """Enqueue one decode step for B branches on the current stream (captured into a graph)."""
+        if self.use_megakernel and B <= 8 and self.tp_world == 1:
+            return self._decode_body_mega(B)
         if self.use_fused and B <= 16 and self.tp_world == 1:
             return self._decode_body_fused(B)
         return self._decode_body_unfused(B)
@@ -372,6 +378,47 @@ class Transformer(nn.Module):
             self._tok_dev[:B].copy_(bufs["logits"].argmax(dim=-1))
             self._pos_dev[:B] += 1
         return bufs["logits"]
+
+    def _build_layer_table(self):
+        """Device array of per-layer pointer records in the order q40_decode_step documents."""
+        rows = []
+        for layer in self.layers:
+            a, f = layer.attention, layer.feed_forward
+            lins = [a.wq, a.wk, a.wv, a.wo, f.w1, f.w3, f.w2]
+            rows.append([l.w.data_ptr() for l in lins] + [l.s.data_ptr() for l in lins] +
+                        [layer.attention_norm.weight.data_ptr(), layer.ffn_norm.weight.data_ptr(),
+                         a.cache_prompt_k.data_ptr(), a.cache_prompt_v.data_ptr(), a.cache_k.data_ptr(),
+                         a.cache_k_s.data_ptr(), a.cache_v.data_ptr(), a.cache_v_s.data_ptr()])
+        self._layer_table = torch.tensor(rows, dtype=torch.int64).to(self.device)
+
+    def _decode_body_mega(self, B):
+        """Decode step for B <= 8 branches as one persistent kernel plus the fp16 lm_head."""
+        p, bufs = self.params, self._step_buffers(B)
+        self._check_loaded()
+        if self._layer_table is None:
+            self._build_layer_table()
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        hid = self.layers[0].feed_forward.hidden_dim
+        sync = bufs["sync"]
+        check(lib.q40_decode_step(self._layer_table.data_ptr(), p.n_layers, B, p.dim, self._H, self._Hkv, hid,
+                                  p.vocab_size, p.max_seq_len, p.max_prompt_seq_len, self._n_pos,
+                                  float(p.norm_eps), self.tok_embeddings.weight.data_ptr(),
+                                  self.norm.weight.data_ptr(), self._tok_dev.data_ptr(), self._pos_dev.data_ptr(),
+                                  self._prefix_len_dev.data_ptr(), self._cos.data_ptr(), self._sin.data_ptr(),
+                                  bufs["h"].data_ptr(), bufs["qkv"].data_ptr(), bufs["ao"].data_ptr(),
+                                  bufs["g"].data_ptr(), bufs["xn"].data_ptr(), bufs["ss_attn"].data_ptr(),
+                                  bufs["ss_ffn"].data_ptr(), sync.data_ptr(), sync.data_ptr() + 4,
+                                  self.max_cluster, st), "q40_decode_step")
+        torch.matmul(bufs["xn"], self.output.weight.t(), out=bufs["logits"])
+        if self.greedy_feedback:
+            self._tok_dev[:B].copy_(bufs["logits"].argmax(dim=-1))
+            self._pos_dev[:B] += 1
+        return bufs["logits"]
+
+    def megakernel_error(self, B) -> int:
+        """Non-zero if a bounded wait inside the persistent step kernel expired (synchronises)."""
+        b = self._bufs.get(B)
+        return 0 if b is None else int(b["sync"][1].item())
 
     def _decode_body_unfused(self, B):
         """One launch per operation; serves any batch width."""
@@ -454,10 +501,11 @@ class Transformer(nn.Module):
         """Run one decode step for B branches with the tokens/positions already in the device
         buffers (`_tok_dev`, `_pos_dev`); returns the static logits buffer [B, vocab]."""
         fused = self.use_fused and B <= 16 and self.tp_world == 1
-        self.launches_per_step = self.params.n_layers * (7 if fused else 13) + (2 if fused else 1)
+        mega = self.use_megakernel and B <= 8 and self.tp_world == 1
+        self.launches_per_step = 1 if mega else self.params.n_layers * (7 if fused else 13) + (2 if fused else 1)
         if not self.use_cuda_graph:
             return self._decode_body(B)
-        key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster)
+        key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster, self.use_megakernel)
         g = self._graphs.get(key)
         if g is None:
             # torch requires capture on a side stream after a warm-up run
@@ -467,11 +515,12 @@ class Transformer(nn.Module):
                 try:
                     self._decode_body(B)
                 except K.Q40Error:
-                    if not (fused and self.max_cluster == 16):
+                    if not ((fused or mega) and self.max_cluster == 16):
                         raise
                     # this device cannot schedule 16-CTA clusters: use the portable size
                     self.max_cluster = 8
-                    key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster)
+                    key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster,
+                           self.use_megakernel)
                     self._decode_body(B)
             torch.cuda.current_stream(self.device).wait_stream(s)
             torch.cuda.synchronize(self.device)

@@ -121,6 +121,39 @@ def test_small_model_matches_oracle_with_forced_cache(small):
         pos += 1
 
 
+def test_megakernel_matches_multi_kernel_path(small):
+    """The persistent whole-step kernel against the multi-kernel fused path on the same model and
+    inputs: same arithmetic and rounding points, different summation order across CTAs, so logits
+    agree within the matmul tolerance step by step (the Q4_0 cache of the second model is
+    overwritten with the first one's rows after every step, see the forced-cache test above)."""
+    g = small
+    mega = build_model(g, True)
+    ref = build_model(g, True)
+    ref.use_megakernel = False
+    assert mega.use_megakernel
+    prompt = torch.from_numpy(g["prompt"]).cuda()
+    l1, l2 = mega(prompt, 0), ref(prompt, 0)
+    assert torch.equal(l1, l2)
+    for B in (1, 3):
+        mega.fork(0, 1, B - 1)
+        ref.fork(0, 1, B - 1)
+        toks = torch.from_numpy(g["first_tokens"][:B]).cuda()
+        pos = prompt.shape[1]
+        for step in range(6):
+            a = mega(toks, pos)[:, -1].float().cpu().numpy()
+            assert mega.megakernel_error(B) == 0
+            b = ref(toks, pos)[:, -1].float().cpu().numpy()
+            logits_close(a, b)
+            for name in ("kq", "ks", "vq", "vs"):
+                ref._caches[name].copy_(mega._caches[name])
+            toks = torch.from_numpy(a.argmax(-1)).view(B, 1).cuda()
+            pos += 1
+        # start the next width from a clean suffix cache
+        for name in ("kq", "ks", "vq", "vs"):
+            mega._caches[name].zero_()
+            ref._caches[name].zero_()
+
+
 def test_fork_copies_suffix_cache(small):
     model = build_model(small, False)
     prompt = torch.from_numpy(small["prompt"]).cuda()
