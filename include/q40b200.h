@@ -145,7 +145,8 @@ int q40_gemv_fused_ss_count(int N, int K, int max_cluster);
  * positions), prefix_len int32 [1], cos/sin fp16 [n_pos, 64].  h/qkv/ao/g/xn, ss_a/ss_f
  * ([M, 1024] floats), bar and err are caller-owned device scratch; bar and err are zeroed on the
  * stream by this call; *err != 0 afterwards means a bounded wait between CTAs expired and the
- * result is undefined.  max_cluster 16 or 8.  Needs an otherwise idle GPU (all CTAs must be
+ * result is undefined.  max_cluster 16 or 8.  `trace` is NULL or a device array of
+ * 6 * n_layers + 8 words that receives the GPU timer after every grid-wide barrier (profiling aid).  Needs an otherwise idle GPU (all CTAs must be
  * resident at once).
  * Replaces: Transformer.forward for one decode step (hf_model_q40_kv_shared.py:492-510). */
 int q40_decode_step(const void* layers, int n_layers, int M, int dim, int H, int Hkv, int hidden,
@@ -153,7 +154,7 @@ int q40_decode_step(const void* layers, int n_layers, int M, int dim, int H, int
                     const void* final_norm, const int64_t* tokens, const int32_t* pos,
                     const int32_t* prefix_len, const void* cos_tbl, const void* sin_tbl, void* h,
                     void* qkv, void* ao, void* g, void* xn, float* ss_a, float* ss_f,
-                    unsigned int* bar, int* err, int max_cluster, void* stream);
+                    unsigned int* bar, int* err, int max_cluster, unsigned long long* trace, void* stream);
 
 /* ---- decode attention (one query token per branch) ---------------------------------- */
 

@@ -77,6 +77,7 @@ struct DsParams {
   unsigned int* bar;   // zeroed by the host before the launch
   int* err;
   int rps_max;      // largest rows-per-split over all phases (sizes the activation staging)
+  unsigned long long* trace;   // optional: CTA 0 stores the global timer after every grid barrier
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -128,9 +129,24 @@ __device__ __forceinline__ void ds_grid_barrier(const DsParams& p, unsigned& gen
       __nanosleep(64);
     }
     __threadfence();
+    if (p.trace && blockIdx.x == 0) {
+      unsigned long long tm;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tm));
+      p.trace[gen] = tm;
+    }
   }
   __syncthreads();
 }
+
+// fine-grained profiling aid: CTA 0, thread 0 stamps the timer into trace[slot]
+#define DS_STAMP(slot)                                                           \
+  do {                                                                           \
+    if (p.trace && blockIdx.x == 0 && threadIdx.x == 0 && layer == 1) {          \
+      unsigned long long tm__;                                                   \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tm__));                   \
+      p.trace[(slot)] = tm__;                                                    \
+    }                                                                            \
+  } while (0)
 
 // --------------------------------------------------------------------------------- weight stream
 enum { PH_QKV = 0, PH_ATTN = 1, PH_WO = 2, PH_W13 = 3, PH_W2 = 4, PH_COUNT = 5 };
@@ -289,6 +305,7 @@ decode_step_kernel(const DsParams p) {
   ds_fill(ring, cur, cur_issued, nxt, nxt_issued, nxt_valid, lane);
 
   unsigned gen = 0;
+  if (p.trace && blockIdx.x == 0 && tid == 0) p.trace[399] = gridDim.x;   // resident CTAs (profiling aid)
   const int M = p.M;
   const int W = (p.H + 2 * p.Hkv) * 128;
   const int cnt_a = g.spans_dim * g.cs;      // partial count of the sums of squares (wo / w2 / embed)
@@ -330,6 +347,7 @@ decode_step_kernel(const DsParams p) {
     for (int ph = 0; ph < PH_COUNT; ++ph) {
       if (ph == PH_ATTN) {
         // ====================== attention: one (branch, head) per cluster ======================
+        DS_STAMP(400 + 16);
         const int plen = min(max(p.prefix_len[0], 0), p.max_p);
         const int rep = p.H / p.Hkv;
         const int grp = tid >> 3, sub = tid & 7;          // 32 key groups of 8 lanes per CTA
@@ -363,6 +381,7 @@ decode_step_kernel(const DsParams p) {
               qf[i] = __half2float(qr) * scale_log2;
             }
           }
+          if (it == g.cluster_id) DS_STAMP(400 + 17);
           float mx = -CUDART_INF_F, l = 0.f, o[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) o[i] = 0.f;
@@ -462,6 +481,7 @@ decode_step_kernel(const DsParams p) {
             if (sub == 0) { L.ks[row * 2] = sk; L.vs[row * 2] = sv; }
             if (sub == 4) { L.ks[row * 2 + 1] = sk; L.vs[row * 2 + 1] = sv; }
           }
+          if (it == g.cluster_id) DS_STAMP(400 + 18);
           // merge the 32 groups of this CTA, then the CTAs of the cluster
           if (sub == 0) { at_m[grp] = mx; at_l[grp] = l; }
 #pragma unroll
@@ -482,6 +502,7 @@ decode_step_kernel(const DsParams p) {
             if (tid == 0) { at_part[0] = Mx; at_part[1] = Ls; }
           }
           cluster.sync();
+          if (it == g.cluster_id) DS_STAMP(400 + 19);
           {
             // rank r finishes dims [r*per, (r+1)*per)
             const int per = 128 / g.cs;
@@ -509,7 +530,9 @@ decode_step_kernel(const DsParams p) {
             }
           }
           cluster.sync();
+          if (it == g.cluster_id) DS_STAMP(400 + 20);
         }
+        DS_STAMP(400 + 21);
         ds_grid_barrier(p, gen);
         continue;
       }
@@ -519,6 +542,7 @@ decode_step_kernel(const DsParams p) {
       ds_split(p, g, ph, K, nsplit, split, rps);
       const int kb = split * rps, ke = min(K, kb + rps);
       const bool has_items = g.cluster_id < ds_items(g, ph);
+      DS_STAMP(400 + ph * 16 + 0);
       if (has_items) {
         // ---- activations of this CTA's k range (same for all its items of the phase) ----
         const __half* src;
@@ -569,6 +593,7 @@ decode_step_kernel(const DsParams p) {
         }
       }
 
+      DS_STAMP(400 + ph * 16 + 1);
       for (int it = g.cluster_id; it < ds_items(g, ph); it += g.ncl) {
         // `cur` describes exactly this item (the stream is walked in the same order)
         float acc[16][4];
@@ -615,6 +640,7 @@ decode_step_kernel(const DsParams p) {
           ++ring.consumed;
           ds_fill(ring, cur, cur_issued, nxt, nxt_issued, nxt_valid, lane);
         }
+        if (it == g.cluster_id) DS_STAMP(400 + ph * 16 + 2);
         // this item's stream is exhausted: the following item becomes current, and the one after it
         // may start to prefetch while this item is reduced
         const int span = (ph == PH_QKV)
@@ -629,6 +655,7 @@ decode_step_kernel(const DsParams p) {
         nxt_issued = 0;
         ds_fill(ring, cur, cur_issued, nxt, nxt_issued, nxt_valid, lane);
 
+        if (it == g.cluster_id) DS_STAMP(400 + ph * 16 + 3);
         // ---- sum the 8 warps: 4-7 store, 0-3 add, then the CTA partial ----
         if (warp >= 4) {
 #pragma unroll
@@ -656,7 +683,9 @@ decode_step_kernel(const DsParams p) {
             cta_part[idx] = sl[off] + sl[off + 16 * 32 * 4] + sl[off + 2 * 16 * 32 * 4] + sl[off + 3 * 16 * 32 * 4];
           }
         }
+        if (it == g.cluster_id) DS_STAMP(400 + ph * 16 + 4);
         cluster.sync();
+        if (it == g.cluster_id) DS_STAMP(400 + ph * 16 + 5);
         {
           const int nranks = g.cs;
           const int slice = DS_SPAN_COLS / nranks;
@@ -718,9 +747,13 @@ decode_step_kernel(const DsParams p) {
             }
           }
         }
+        if (it == g.cluster_id) DS_STAMP(400 + ph * 16 + 6);
         cluster.sync();
+        if (it == g.cluster_id) DS_STAMP(400 + ph * 16 + 7);
       }
+      DS_STAMP(400 + ph * 16 + 8);
       ds_grid_barrier(p, gen);
+      DS_STAMP(400 + ph * 16 + 9);
     }
   }
 
@@ -767,7 +800,7 @@ extern "C" int q40_decode_step(const void* layers, int n_layers, int M, int dim,
                                const void* final_norm, const int64_t* tokens, const int32_t* pos,
                                const int32_t* prefix_len, const void* cos_tbl, const void* sin_tbl, void* h,
                                void* qkv, void* ao, void* g, void* xn, float* ss_a, float* ss_f,
-                               unsigned int* bar, int* err, int max_cluster, void* stream) {
+                               unsigned int* bar, int* err, int max_cluster, unsigned long long* trace, void* stream) {
   using namespace q40;
   if (!layers || !emb || !final_norm || !tokens || !pos || !prefix_len || !cos_tbl || !sin_tbl || !h || !qkv ||
       !ao || !g || !xn || !ss_a || !ss_f || !bar || !err)
@@ -821,7 +854,7 @@ extern "C" int q40_decode_step(const void* layers, int n_layers, int M, int dim,
   p.tokens = tokens; p.pos = pos; p.prefix_len = prefix_len;
   p.cos_tbl = (const __half*)cos_tbl; p.sin_tbl = (const __half*)sin_tbl;
   p.h = (__half*)h; p.qkv = (__half*)qkv; p.ao = (__half*)ao; p.g = (__half*)g; p.xn = (__half*)xn;
-  p.ss_a = ss_a; p.ss_f = ss_f; p.bar = bar; p.err = err; p.rps_max = rps_max;
+  p.ss_a = ss_a; p.ss_f = ss_f; p.bar = bar; p.err = err; p.rps_max = rps_max; p.trace = trace;
   e = cudaLaunchKernelEx(&cfg, decode_step_kernel, p);
   if (e != cudaSuccess) return (int)e;
   return Q40_OK;

@@ -214,6 +214,7 @@ class Transformer(nn.Module):
         # B <= 8 without tensor parallelism can run the whole step as one persistent kernel
         self.use_megakernel = True
         self._layer_table = None
+        self._trace = None       # optional int64 tensor [6 * n_layers + 8]: barrier timestamps of the step kernel
 
     # ------------------------------------------------------------------ reference API
     @torch.inference_mode()
@@ -408,7 +409,8 @@ class Transformer(nn.Module):
                                   bufs["h"].data_ptr(), bufs["qkv"].data_ptr(), bufs["ao"].data_ptr(),
                                   bufs["g"].data_ptr(), bufs["xn"].data_ptr(), bufs["ss_attn"].data_ptr(),
                                   bufs["ss_ffn"].data_ptr(), sync.data_ptr(), sync.data_ptr() + 4,
-                                  self.max_cluster, st), "q40_decode_step")
+                                  self.max_cluster, self._trace.data_ptr() if self._trace is not None else None,
+                                  st), "q40_decode_step")
         torch.matmul(bufs["xn"], self.output.weight.t(), out=bufs["logits"])
         if self.greedy_feedback:
             self._tok_dev[:B].copy_(bufs["logits"].argmax(dim=-1))
