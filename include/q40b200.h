@@ -134,6 +134,23 @@ int q40_gemv_fused(int mode, int nmat, const void* const* bw, const void* const*
                    void* stream);
 int q40_gemv_fused_ss_count(int N, int K, int max_cluster);
 
+/* Tiled copy of a packed [K, N] matrix for q40_gemv_tiled (N % 256 == 0, K % 16 == 0): a one-time
+ * device pass that rearranges codes and scales (none is changed) so that the decode matmul needs
+ * about one instruction per weight.  `out` has q40_tiled_bytes(N, K) bytes (= packed + scales).
+ * No counterpart in the reference (its Triton kernel reads the checkpoint layout directly). */
+size_t q40_tiled_bytes(int N, int K);
+int q40_relayout_tiled(const void* bw, const void* bs, void* out, int N, int K, void* stream);
+
+/* q40_gemv_fused on tiled copies (same modes, arguments and results up to rounding: the scale is
+ * applied to the activations, fp16(scale*x), instead of to the weight; 1 <= M <= 8; every
+ * N % 256 == 0).  bw[i] are the tiled streams; bs is ignored and may be NULL. */
+int q40_gemv_tiled(int mode, int nmat, const void* const* bw, const void* const* bs, void* const* out,
+                   const int* n_cols, int64_t ldc, const void* a, int64_t lda, int M, int K,
+                   const void* norm_w, const float* ss_in, int ss_in_count, float eps, const void* h_in,
+                   int64_t ldh, float* ss_out, int ss_out_count, int max_cluster, int use_pdl,
+                   void* stream);
+int q40_gemv_tiled_ss_count(int N, int K, int max_cluster);
+
 /* One whole decode step of the KV-shared Q4_0 model for 1 <= M <= 8 branches as a single
  * persistent launch: embedding, every layer ([wq,wk,wv] with RMSNorm, rotary embedding + Q4_0
  * cache append + attention over shared prompt / packed suffix / new token, wo + residual,

@@ -22,7 +22,7 @@ __all__ = [
     "quantize_q40", "dequantize_q40", "triton_deq_int40", "triton_q_int40", "triton_q_int40_sliced",
     "quantize_q40_rows", "matmul", "matmul_q40", "linear_q40", "flash_attn", "page_flash_attn",
     "triton_attn", "chunk_attn", "shared_prefix_attn", "matmul_split_k", "rmsnorm", "rope_", "silu_mul",
-    "gemv_fused", "embed_rows", "tc_error_flag",
+    "gemv_fused", "embed_rows", "tc_error_flag", "relayout_tiled",
     "Q40Error",
 ]
 
@@ -208,14 +208,27 @@ def linear_q40(x: torch.Tensor, w_q: torch.Tensor, w_s: torch.Tensor, w_shape, *
     return y.view(*lead, N)
 
 
+def relayout_tiled(b_w: torch.Tensor, b_s: torch.Tensor, b_shape) -> torch.Tensor:
+    """Tiled copy (uint8 tensor) of a packed [K, N] matrix for gemv_fused(..., tiled=True)."""
+    dev = _need_cuda(b_w, b_s)
+    K, N = int(b_shape[0]), int(b_shape[1])
+    nbytes = lib.q40_tiled_bytes(N, K)
+    if nbytes == 0:
+        raise Q40Error(f"relayout_tiled: shape ({K}, {N}) needs N % 256 == 0 and K % 16 == 0")
+    out = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    check(lib.q40_relayout_tiled(b_w.contiguous().data_ptr(), b_s.contiguous().data_ptr(), out.data_ptr(), N, K,
+                                 _stream(dev)), "q40_relayout_tiled")
+    return out
+
+
 def gemv_fused(mode: int, a: torch.Tensor, weights, *, norm_w=None, ss_in=None, eps: float = 1e-5, h_in=None,
-               max_cluster: int = 16, use_pdl: bool = False):
+               max_cluster: int = 16, use_pdl: bool = False, tiled: bool = False):
     """Decode-step matmul(s) with fused neighbours (q40_gemv_fused in include/q40b200.h).
     `weights` is a list of 1-3 (b_w, b_s, (K, N)) triples sharing the activations a [M <= 16, K].
     mode 0: [a @ deq(B_i)]; 1: RMSNorm(a; norm_w, ss_in) first; 2: returns (h_in + a @ deq(B),
     ss_out [M, count]); 3: silu(RMSNorm(a) @ deq(B_0)) * (RMSNorm(a) @ deq(B_1))."""
     import ctypes
-    dev = _need_cuda(a, norm_w, ss_in, h_in, *[w[0] for w in weights], *[w[1] for w in weights])
+    dev = _need_cuda(a, norm_w, ss_in, h_in, *[w[0] for w in weights], *[w[1] for w in weights if w[1] is not None])
     M, K = a.shape
     n = len(weights)
     Ns = [int(w[2][1]) for w in weights]
@@ -235,16 +248,18 @@ def gemv_fused(mode: int, a: torch.Tensor, weights, *, norm_w=None, ss_in=None, 
             outs.append(buf[:, c0:c0 + N])
             c0 += N
         ldc = sum(Ns)
+    fn = lib.q40_gemv_tiled if tiled else lib.q40_gemv_fused
     ss_out, cnt = None, 0
     if mode == 2:
-        cnt = lib.q40_gemv_fused_ss_count(Ns[0], K, max_cluster)
+        cnt = (lib.q40_gemv_tiled_ss_count if tiled else lib.q40_gemv_fused_ss_count)(Ns[0], K, max_cluster)
         ss_out = torch.empty((M, cnt), dtype=torch.float32, device=dev)
     a = a.contiguous()
-    check(lib.q40_gemv_fused(mode, n, P(*[w[0].data_ptr() for w in weights]), P(*[w[1].data_ptr() for w in weights]),
+    check(fn(mode, n, P(*[w[0].data_ptr() for w in weights]),
+             P(*[(w[1].data_ptr() if w[1] is not None else 0) for w in weights]),
                              P(*[o.data_ptr() for o in outs]), (ctypes.c_int * n)(*Ns), ldc, a.data_ptr(),
                              a.stride(0), M, K, _ptr(norm_w), _ptr(ss_in), ss_in.shape[1] if ss_in is not None else 0,
                              float(eps), _ptr(h_in), h_in.stride(0) if h_in is not None else 0, _ptr(ss_out), cnt,
-                             max_cluster, 1 if use_pdl else 0, _stream(dev)), "q40_gemv_fused")
+             max_cluster, 1 if use_pdl else 0, _stream(dev)), "q40_gemv_fused")
     if mode == 2:
         return outs[0], ss_out
     if mode == 3:

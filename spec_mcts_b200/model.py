@@ -212,7 +212,9 @@ class Transformer(nn.Module):
         self.use_pdl = True
         self.max_cluster = 16
         # B <= 8 without tensor parallelism can run the whole step as one persistent kernel
-        self.use_megakernel = True
+        self.use_megakernel = False
+        # B <= 8: the fused matmuls read a rearranged ("tiled") copy of each weight, made on first use
+        self.use_tiled = True
         self._layer_table = None
         self._trace = None       # optional int64 tensor [6 * n_layers + 8]: barrier timestamps of the step kernel
 
@@ -321,12 +323,21 @@ class Transformer(nn.Module):
         import ctypes
         n = len(lins)
         P = ctypes.c_void_p * n
-        bw = P(*[l.w.data_ptr() for l in lins])
+        tiled = self.use_tiled and M <= 8 and all(l.kn()[1] % 256 == 0 and l.kn()[0] % 16 == 0 for l in lins)
+        if tiled:
+            for l in lins:
+                if getattr(l, "_tiled", None) is None or l._tiled_src != l.w.data_ptr():
+                    l._tiled = K.relayout_tiled(l.w, l.s, l.kn())     # one-time rearranged copy
+                    l._tiled_src = l.w.data_ptr()
+            bw = P(*[l._tiled.data_ptr() for l in lins])
+        else:
+            bw = P(*[l.w.data_ptr() for l in lins])
         bs = P(*[l.s.data_ptr() for l in lins])
+        fn = lib.q40_gemv_tiled if tiled else lib.q40_gemv_fused
         op = P(*[o.data_ptr() for o in outs])
         nc = (ctypes.c_int * n)(*[l.kn()[1] for l in lins])
         Kd = lins[0].kn()[0]
-        check(lib.q40_gemv_fused(mode, n, bw, bs, op, nc, ldc, a.data_ptr(), lda, M, Kd,
+        check(fn(mode, n, bw, bs, op, nc, ldc, a.data_ptr(), lda, M, Kd,
                                  norm_w.data_ptr() if norm_w is not None else None,
                                  ss_in.data_ptr() if ss_in is not None else None, ss_in_count,
                                  float(self.params.norm_eps), h_in.data_ptr() if h_in is not None else None, ldh,
@@ -507,7 +518,8 @@ class Transformer(nn.Module):
         self.launches_per_step = 1 if mega else self.params.n_layers * (7 if fused else 13) + (2 if fused else 1)
         if not self.use_cuda_graph:
             return self._decode_body(B)
-        key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster, self.use_megakernel)
+        key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster, self.use_megakernel,
+               self.use_tiled)
         g = self._graphs.get(key)
         if g is None:
             # torch requires capture on a side stream after a warm-up run
@@ -522,7 +534,7 @@ class Transformer(nn.Module):
                     # this device cannot schedule 16-CTA clusters: use the portable size
                     self.max_cluster = 8
                     key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster,
-                           self.use_megakernel)
+                           self.use_megakernel, self.use_tiled)
                     self._decode_body(B)
             torch.cuda.current_stream(self.device).wait_stream(s)
             torch.cuda.synchronize(self.device)

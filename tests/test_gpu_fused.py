@@ -56,13 +56,37 @@ def test_mode0_three_matrices(K, M, KN, cluster):
         close(o.cpu().numpy(), O.matmul_q40(a, q, s, (Kd, n)))
 
 
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("KN", [(512, 256), (4096, 4096), (4096, 11008), (11008, 4096), (1024, 768)])
+def test_tiled_mode0_and_relayout(K, M, KN):
+    """The rearranged weight copy: mode 0 on tiled streams against the oracle and against the
+    checkpoint-layout kernel."""
+    Kd, N = KN
+    rng = np.random.default_rng(Kd + N + M + 1)
+    Ns = [N, 256] if Kd * N < 5e6 else [N]
+    mats = [qmat(rng, Kd, n, 0.5 / np.sqrt(Kd / 256)) for n in Ns]
+    a = (rng.standard_normal((M, Kd)) * 0.5).astype(np.float16)
+    dm = [(dev(q), dev(s)) for q, s in mats]
+    tl = [(K.relayout_tiled(q, s, (Kd, n)), None, (Kd, n)) for (q, s), n in zip(dm, Ns)]
+    assert tl[0][0].numel() == mats[0][0].size + mats[0][1].size * 2      # same bytes as packed + scales
+    outs = K.gemv_fused(0, dev(a), tl, tiled=True)
+    for o, (q, s), n in zip(outs, mats, Ns):
+        close(o.cpu().numpy(), O.matmul_q40(a, q, s, (Kd, n)))
+    ref = K.gemv_fused(0, dev(a), [(q, s, (Kd, n)) for (q, s), n in zip(dm, Ns)])
+    for o, r in zip(outs, ref):
+        close(o.cpu().numpy(), r.cpu().numpy(), rtol=1e-2, atol=3e-3)
+
+
+@pytest.mark.parametrize("tiled", [False, True])
 @pytest.mark.parametrize("M", [1, 3, 10, 16])
 @pytest.mark.parametrize("dims", [(512, 768), (4096, 11008)])
-def test_layer_chain_modes_1_2_3(K, M, dims):
+def test_layer_chain_modes_1_2_3(K, M, dims, tiled):
     """embed -> [norm+qkv] -> wo(+residual) -> [norm + w1/w3 + silu-mul] -> w2(+residual), each
     stage against the oracle computed from the GPU's own previous stage (so tolerances do not
     compound), with programmatic dependent launch on."""
     dim, hid = dims
+    if tiled and M > 8:
+        pytest.skip("the tiled kernels serve up to 8 rows")
     rng = np.random.default_rng(dim + M)
     sd = 0.5 / np.sqrt(dim / 256)
     wq, wk, wo = qmat(rng, dim, dim, sd), qmat(rng, dim, 256, sd), qmat(rng, dim, dim, sd)
@@ -70,32 +94,35 @@ def test_layer_chain_modes_1_2_3(K, M, dims):
     emb = (rng.standard_normal((100, dim)) * 0.7).astype(np.float16)
     nw = (1 + 0.1 * rng.standard_normal(dim)).astype(np.float16)
     toks = rng.integers(0, 100, size=M)
-    D = lambda qs, kn: (dev(qs[0]), dev(qs[1]), kn)
-    c_ffn = K.lib.q40_gemv_fused_ss_count(dim, hid, 16)
+    if tiled:
+        D = lambda qs, kn: (K.relayout_tiled(dev(qs[0]), dev(qs[1]), kn), None, kn)
+    else:
+        D = lambda qs, kn: (dev(qs[0]), dev(qs[1]), kn)
+    c_ffn = (K.lib.q40_gemv_tiled_ss_count if tiled else K.lib.q40_gemv_fused_ss_count)(dim, hid, 16)
     h, ss = K.embed_rows(dev(emb), dev(toks), c_ffn)
     h_np = emb[toks]
     np.testing.assert_array_equal(h.cpu().numpy(), h_np)
     np.testing.assert_allclose(ss.cpu().numpy().sum(1), (h_np.astype(np.float32) ** 2).sum(1), rtol=1e-5)
     # mode 1
-    q, k = K.gemv_fused(1, h, [D(wq, (dim, dim)), D(wk, (dim, 256))], norm_w=dev(nw), ss_in=ss, use_pdl=True)
+    q, k = K.gemv_fused(1, h, [D(wq, (dim, dim)), D(wk, (dim, 256))], norm_w=dev(nw), ss_in=ss, use_pdl=True, tiled=tiled)
     xn = O.rmsnorm(h_np, nw, 1e-5)
     close(q.cpu().numpy(), O.matmul_q40(xn, *wq, (dim, dim)))
     close(k.cpu().numpy(), O.matmul_q40(xn, *wk, (dim, 256)))
     # mode 2 (in place on a copy of h)
     ao = (rng.standard_normal((M, dim)) * 0.5).astype(np.float16)
-    h2, ss2 = K.gemv_fused(2, dev(ao), [D(wo, (dim, dim))], h_in=h, use_pdl=True)
+    h2, ss2 = K.gemv_fused(2, dev(ao), [D(wo, (dim, dim))], h_in=h, use_pdl=True, tiled=tiled)
     h2_np = h2.cpu().numpy()
     ref = (h_np.astype(np.float32) + O.matmul_q40(ao, *wo, (dim, dim)).astype(np.float32)).astype(np.float16)
     close(h2_np, ref)
     np.testing.assert_allclose(ss2.cpu().numpy().sum(1), (h2_np.astype(np.float32) ** 2).sum(1), rtol=1e-4)
     # mode 3 from the GPU's h2 / ss2
-    g = K.gemv_fused(3, h2, [D(w1, (dim, hid)), D(w3, (dim, hid))], norm_w=dev(nw), ss_in=ss2, use_pdl=True)
+    g = K.gemv_fused(3, h2, [D(w1, (dim, hid)), D(w3, (dim, hid))], norm_w=dev(nw), ss_in=ss2, use_pdl=True, tiled=tiled)
     xn2 = O.rmsnorm(h2_np, nw, 1e-5)
     gref = O.silu_mul(O.matmul_q40(xn2, *w1, (dim, hid)), O.matmul_q40(xn2, *w3, (dim, hid)))
     close(g.cpu().numpy(), gref, rtol=3e-2, atol=2e-2)
     # mode 2 again (w2), in place
     g_np = g.cpu().numpy()
-    h3, ss3 = K.gemv_fused(2, g, [D(w2, (hid, dim))], h_in=h2, use_pdl=True)
+    h3, ss3 = K.gemv_fused(2, g, [D(w2, (hid, dim))], h_in=h2, use_pdl=True, tiled=tiled)
     ref3 = (h2_np.astype(np.float32) + O.matmul_q40(g_np, *w2, (hid, dim)).astype(np.float32)).astype(np.float16)
     close(h3.cpu().numpy(), ref3)
     assert ss3.shape[1] == c_ffn

@@ -128,9 +128,10 @@ def test_megakernel_matches_multi_kernel_path(small):
     overwritten with the first one's rows after every step, see the forced-cache test above)."""
     g = small
     mega = build_model(g, True)
+    mega.use_megakernel = True
     ref = build_model(g, True)
     ref.use_megakernel = False
-    assert mega.use_megakernel
+    ref.use_tiled = False
     prompt = torch.from_numpy(g["prompt"]).cuda()
     l1, l2 = mega(prompt, 0), ref(prompt, 0)
     assert torch.equal(l1, l2)
