@@ -230,6 +230,17 @@ int q40_attn_tree_decode(const void* q, int64_t q_stride, const void* prefix_k, 
                          const void* cur_v, int64_t cur_stride, void* o, int B, int H, int Hkv, int D,
                          void* workspace, size_t workspace_bytes, void* stream);
 
+/* q40_rope_kv_append + q40_attn_tree_decode as one launch for small widths (a cluster of 8 CTAs
+ * per (branch, head) splits the keys; no workspace): qkv [B, W] holds the new token's q heads, k
+ * heads and v heads (un-rotated, W >= (H + 2 Hkv) * 128); the rotated key and the value are
+ * appended to the Q4_0 suffix cache at slot (b, pos[b] - *prefix_len) and the attention output is
+ * written to ao [B, H*128].  Caches and tables as in the two calls it replaces.
+ * Replaces: the decode branch of Attention.forward (hf_model_q40_kv_shared.py:313-317, 330-405). */
+int q40_attn_tree_fused(void* qkv, int64_t W, const void* pk, const void* pv, void* kq, void* ks, void* vq,
+                        void* vs, const int32_t* pos, const int32_t* prefix_len, const void* cos_tbl,
+                        const void* sin_tbl, int n_pos, void* ao, int B, int H, int Hkv, int D, int max_t,
+                        int max_p, void* stream);
+
 /* Rotary embedding of the new token's q [B, H*D] and k [B, Hkv*D] in place (position
  * pos_dev[b], tables cos/sin [n_pos, D/2] fp16) and Q4_0 append of the rotated k and of v to
  * the suffix cache at slot (b, pos_dev[b] - *prefix_len_dev); k and v stay un-quantised in

@@ -1,0 +1,271 @@
+// Decode attention of the KV-shared model as ONE launch: rotary embedding of q and of the new key,
+// Q4_0 append of the new key/value, and attention over [shared fp16 prompt | packed Q4_0 suffix |
+// the un-quantised new token].  A thread-block cluster of 8 CTAs serves one (branch, head): its
+// 256 groups of 8 lanes take the keys round-robin (each lane owns 16 of the 128 head dims), every
+// group keeps an fp32 online-softmax state, groups are merged through shared memory inside a
+// CTA and the CTAs through distributed shared memory, each rank finishing 16 output dims.
+// Meant for small widths (up to about 16 branches), where three separate launches (rotary+append,
+// shared-prefix MMA pass, per-branch pass) cost more than the attention itself; larger widths
+// use q40_attn_tree_decode, which reads the prompt once for all branches.
+//
+// Reference: Attention.forward decode branch (hf_model_q40_kv_shared.py:313-317, 330-405).
+#include <cooperative_groups.h>
+#include <math_constants.h>
+
+#include "q40_common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace q40 {
+
+constexpr int TF_THREADS = 256;
+constexpr int TF_CLUSTER = 8;
+
+struct TreeFusedArgs {
+  __half* qkv;             // [B, W]: q heads, then k heads, then v heads of the new token (un-rotated)
+  int64_t W;
+  const __half* pk;        // prompt cache [max_p, Hkv, 128]
+  const __half* pv;
+  int8_t* kq;              // suffix cache [maxB, max_t, Hkv, 64]
+  __half* ks;
+  int8_t* vq;
+  __half* vs;
+  const int32_t* pos;
+  const int32_t* prefix_len;
+  const __half* cos_tbl;   // [n_pos, 64]
+  const __half* sin_tbl;
+  __half* ao;              // [B, H*128]
+  int H, Hkv, max_t, max_p, n_pos;
+};
+
+__global__ void __cluster_dims__(TF_CLUSTER, 1, 1) __launch_bounds__(TF_THREADS)
+attn_tree_fused_kernel(const TreeFusedArgs a) {
+  cg::cluster_group cluster = cg::this_cluster();
+  asm volatile("griddepcontrol.launch_dependents;");
+  __shared__ float at_m[32], at_l[32];
+  __shared__ __align__(16) float at_o[32 * 128];
+  __shared__ __align__(16) float at_part[132];
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int cs = TF_CLUSTER;
+  const int rank = (int)cluster.block_rank();
+  const int it = blockIdx.x / TF_CLUSTER;
+  const int b = it / a.H, hq = it % a.H;
+  const int rep = a.H / a.Hkv, hk = hq / rep;
+  const int grp = tid >> 3, sub = tid & 7;
+  const unsigned gmask = 0xffu << (lane & 24);
+  const int ngroups = 32 * cs;
+  const int gidx = rank * 32 + grp;
+  const float scale_log2 = (1.0f / sqrtf(128.0f)) * 1.4426950408889634f;
+  const int plen = min(max(a.prefix_len[0], 0), a.max_p);
+  int pos = a.pos[b];
+  pos = min(max(pos, 0), a.n_pos - 1);
+  const int slen = min(max(pos - plen, 0), a.max_t);
+
+  // this lane's 16 dims of the rotated, pre-scaled query and of the rotated new key; its 16 dims of v
+  float qf[16];
+  __align__(16) __half kc[16], vc[16];
+  {
+    const __half* qp = a.qkv + (int64_t)b * a.W + hq * 128;
+    const __half* kp = a.qkv + (int64_t)b * a.W + (a.H + hk) * 128;
+    const __half* vp = a.qkv + (int64_t)b * a.W + (a.H + a.Hkv + hk) * 128;
+    const int d0 = sub * 16, dp = (d0 + 64) & 127;
+    const bool lo_half = d0 < 64;
+    __align__(16) __half q1[16], q2[16], k1[16], k2[16], cs_[16], sn_[16];
+    *reinterpret_cast<uint4*>(q1) = *reinterpret_cast<const uint4*>(qp + d0);
+    *reinterpret_cast<uint4*>(q1 + 8) = *reinterpret_cast<const uint4*>(qp + d0 + 8);
+    *reinterpret_cast<uint4*>(q2) = *reinterpret_cast<const uint4*>(qp + dp);
+    *reinterpret_cast<uint4*>(q2 + 8) = *reinterpret_cast<const uint4*>(qp + dp + 8);
+    *reinterpret_cast<uint4*>(k1) = *reinterpret_cast<const uint4*>(kp + d0);
+    *reinterpret_cast<uint4*>(k1 + 8) = *reinterpret_cast<const uint4*>(kp + d0 + 8);
+    *reinterpret_cast<uint4*>(k2) = *reinterpret_cast<const uint4*>(kp + dp);
+    *reinterpret_cast<uint4*>(k2 + 8) = *reinterpret_cast<const uint4*>(kp + dp + 8);
+    *reinterpret_cast<uint4*>(vc) = *reinterpret_cast<const uint4*>(vp + d0);
+    *reinterpret_cast<uint4*>(vc + 8) = *reinterpret_cast<const uint4*>(vp + d0 + 8);
+    const __half* ct = a.cos_tbl + (int64_t)pos * 64 + (d0 & 63);
+    const __half* st = a.sin_tbl + (int64_t)pos * 64 + (d0 & 63);
+    *reinterpret_cast<uint4*>(cs_) = *reinterpret_cast<const uint4*>(ct);
+    *reinterpret_cast<uint4*>(cs_ + 8) = *reinterpret_cast<const uint4*>(ct + 8);
+    *reinterpret_cast<uint4*>(sn_) = *reinterpret_cast<const uint4*>(st);
+    *reinterpret_cast<uint4*>(sn_ + 8) = *reinterpret_cast<const uint4*>(st + 8);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      // out = x*cos + rot(x)*sin, rot(x) = -partner for the low half of the head, +partner for the high half
+      const __half qr = __hadd_rn(__hmul_rn(q1[i], cs_[i]), __hmul_rn(lo_half ? __hneg(q2[i]) : q2[i], sn_[i]));
+      kc[i] = __hadd_rn(__hmul_rn(k1[i], cs_[i]), __hmul_rn(lo_half ? __hneg(k2[i]) : k2[i], sn_[i]));
+      qf[i] = __half2float(qr) * scale_log2;
+    }
+  }
+          float mx = -CUDART_INF_F, l = 0.f, o[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) o[i] = 0.f;
+  // keys: [0, plen) prompt (fp16), [plen, plen + slen) suffix (Q4_0), then the new token
+  const int total_keys = plen + slen + 1;
+  for (int key = gidx; key < total_keys; key += ngroups) {
+    float kv_k[16], kv_v[16];
+    if (key < plen) {
+      const int64_t off = ((int64_t)key * a.Hkv + hk) * 128 + sub * 16;
+      const uint4 k0 = __ldg(reinterpret_cast<const uint4*>(a.pk + off));
+      const uint4 k1 = __ldg(reinterpret_cast<const uint4*>(a.pk + off + 8));
+      const uint4 v0 = __ldg(reinterpret_cast<const uint4*>(a.pv + off));
+      const uint4 v1 = __ldg(reinterpret_cast<const uint4*>(a.pv + off + 8));
+      const __half2* a0 = reinterpret_cast<const __half2*>(&k0);
+      const __half2* a1 = reinterpret_cast<const __half2*>(&k1);
+      const __half2* c0 = reinterpret_cast<const __half2*>(&v0);
+      const __half2* c1 = reinterpret_cast<const __half2*>(&v1);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 f = __half22float2(a0[i]); kv_k[2 * i] = f.x; kv_k[2 * i + 1] = f.y;
+        f = __half22float2(a1[i]); kv_k[8 + 2 * i] = f.x; kv_k[8 + 2 * i + 1] = f.y;
+        f = __half22float2(c0[i]); kv_v[2 * i] = f.x; kv_v[2 * i + 1] = f.y;
+        f = __half22float2(c1[i]); kv_v[8 + 2 * i] = f.x; kv_v[8 + 2 * i + 1] = f.y;
+      }
+    } else if (key < plen + slen) {
+      const int64_t row = ((int64_t)b * a.max_t + (key - plen)) * a.Hkv + hk;
+      const int nib_lo = sub >> 2, boff = 16 * (sub & 3);
+      const uint4 kb4 = __ldg(reinterpret_cast<const uint4*>(a.kq + row * 64 + boff));
+      const uint4 vb4 = __ldg(reinterpret_cast<const uint4*>(a.vq + row * 64 + boff));
+      const __half2 ksc = __half2half2(a.ks[row * 2 + nib_lo]);
+      const __half2 vsc = __half2half2(a.vs[row * 2 + nib_lo]);
+      const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kb4);
+      const uint32_t* vw = reinterpret_cast<const uint32_t*>(&vb4);
+#pragma unroll
+      for (int wi = 0; wi < 4; ++wi) {
+        const uint32_t a = nib_lo ? kw[wi] : (kw[wi] >> 4);
+        const uint32_t c = nib_lo ? vw[wi] : (vw[wi] >> 4);
+        float2 f = __half22float2(__hmul2(codes_lo_to_h2(a), ksc));
+        kv_k[4 * wi] = f.x; kv_k[4 * wi + 2] = f.y;
+        f = __half22float2(__hmul2(codes_lo_to_h2(a >> 8), ksc));
+        kv_k[4 * wi + 1] = f.x; kv_k[4 * wi + 3] = f.y;
+        f = __half22float2(__hmul2(codes_lo_to_h2(c), vsc));
+        kv_v[4 * wi] = f.x; kv_v[4 * wi + 2] = f.y;
+        f = __half22float2(__hmul2(codes_lo_to_h2(c >> 8), vsc));
+        kv_v[4 * wi + 1] = f.x; kv_v[4 * wi + 3] = f.y;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) { kv_k[i] = __half2float(kc[i]); kv_v[i] = __half2float(vc[i]); }
+    }
+    float sdot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) sdot = fmaf(qf[i], kv_k[i], sdot);
+    sdot += __shfl_xor_sync(gmask, sdot, 1);
+    sdot += __shfl_xor_sync(gmask, sdot, 2);
+    sdot += __shfl_xor_sync(gmask, sdot, 4);
+    const float mnew = fmaxf(mx, sdot);
+    const float corr = exp2f(mx - mnew), pw = exp2f(sdot - mnew);
+    l = l * corr + pw;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) o[i] = fmaf(pw, kv_v[i], o[i] * corr);
+    mx = mnew;
+  }
+  // Q4_0 append of the new token's rotated key and its value: the first query head of a kv
+  // group, rank 0, key group 0 (the 8 lanes hold the whole 128-dim row)
+  if (rank == 0 && grp == 0 && (hq % rep) == 0 && (pos - plen) >= 0 && (pos - plen) < a.max_t) {
+    float ak = 0.f, av = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      ak = fmaxf(ak, fabsf(__half2float(kc[i])));
+      av = fmaxf(av, fabsf(__half2float(vc[i])));
+    }
+    // a 64-dim group is lanes sub 0..3 (dims 0..63) or 4..7 (dims 64..127)
+    ak = fmaxf(ak, __shfl_xor_sync(0xffu, ak, 1)); ak = fmaxf(ak, __shfl_xor_sync(0xffu, ak, 2));
+    av = fmaxf(av, __shfl_xor_sync(0xffu, av, 1)); av = fmaxf(av, __shfl_xor_sync(0xffu, av, 2));
+    const __half sk = __float2half_rn(__fdiv_rn(ak, 7.0f)), sv = __float2half_rn(__fdiv_rn(av, 7.0f));
+    const float fk = __half2float(sk), fv = __half2float(sv);
+    uint32_t ck[4] = {0, 0, 0, 0}, cv[4] = {0, 0, 0, 0};     // this lane's 16 codes, one nibble each
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float a = rintf(__half2float(__float2half_rn(__fdiv_rn(__half2float(kc[i]), fk))));
+      float c = rintf(__half2float(__float2half_rn(__fdiv_rn(__half2float(vc[i]), fv))));
+      const int ia = (fabsf(a) <= 65504.0f) ? (int)a : 0, ic = (fabsf(c) <= 65504.0f) ? (int)c : 0;
+      ck[i >> 2] |= (uint32_t)(ia & 0xF) << (8 * (i & 3));
+      cv[i >> 2] |= (uint32_t)(ic & 0xF) << (8 * (i & 3));
+    }
+    // byte d = code(dim d) << 4 | code(dim d + 64): lanes sub and sub + 4 combine
+    const int64_t row = ((int64_t)b * a.max_t + (pos - plen)) * a.Hkv + hk;
+#pragma unroll
+    for (int wi = 0; wi < 4; ++wi) {
+      const uint32_t ok_ = __shfl_xor_sync(0xffu, ck[wi], 4), ov_ = __shfl_xor_sync(0xffu, cv[wi], 4);
+      if (sub < 4) {
+        reinterpret_cast<uint32_t*>(a.kq + row * 64 + 16 * sub)[wi] = (ck[wi] << 4) | ok_;
+        reinterpret_cast<uint32_t*>(a.vq + row * 64 + 16 * sub)[wi] = (cv[wi] << 4) | ov_;
+      }
+    }
+    if (sub == 0) { a.ks[row * 2] = sk; a.vs[row * 2] = sv; }
+    if (sub == 4) { a.ks[row * 2 + 1] = sk; a.vs[row * 2 + 1] = sv; }
+  }
+
+          if (sub == 0) { at_m[grp] = mx; at_l[grp] = l; }
+#pragma unroll
+  for (int i = 0; i < 16; i += 4)
+    *reinterpret_cast<float4*>(&at_o[grp * 128 + sub * 16 + i]) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+  __syncthreads();
+  if (tid < 128) {
+    float Mx = -CUDART_INF_F;
+    for (int q = 0; q < 32; ++q) Mx = fmaxf(Mx, at_m[q]);
+    float Ls = 0.f, acc = 0.f;
+    if (Mx > -CUDART_INF_F)
+      for (int q = 0; q < 32; ++q) {
+        const float w = exp2f(at_m[q] - Mx);
+        Ls = fmaf(at_l[q], w, Ls);
+        acc = fmaf(at_o[q * 128 + tid], w, acc);
+      }
+    at_part[2 + tid] = acc;
+    if (tid == 0) { at_part[0] = Mx; at_part[1] = Ls; }
+  }
+  cluster.sync();
+  {
+    // rank r finishes dims [r*per, (r+1)*per)
+    const int per = 128 / cs;
+    if (tid < per) {
+      const int d = rank * per + tid;
+      float pm[16], pl[16], po[16];
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        if (r < cs) {
+          const float* rp = cluster.map_shared_rank(at_part, r);
+          pm[r] = rp[0]; pl[r] = rp[1]; po[r] = rp[2 + d];
+        } else { pm[r] = -CUDART_INF_F; pl[r] = 0.f; po[r] = 0.f; }
+      }
+      float Mx = -CUDART_INF_F;
+#pragma unroll
+      for (int r = 0; r < 16; ++r) Mx = fmaxf(Mx, pm[r]);
+      float Ls = 0.f, acc = 0.f;
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        const float w = (pm[r] > -CUDART_INF_F) ? exp2f(pm[r] - Mx) : 0.f;
+        Ls = fmaf(pl[r], w, Ls);
+        acc = fmaf(po[r], w, acc);
+      }
+      a.ao[(int64_t)b * (a.H * 128) + hq * 128 + d] = __float2half_rn(Ls > 0.f ? acc / Ls : 0.f);
+    }
+  }
+  cluster.sync();   // nobody leaves while a neighbour may still read its partial
+}
+
+}  // namespace q40
+
+extern "C" int q40_attn_tree_fused(void* qkv, int64_t W, const void* pk, const void* pv, void* kq, void* ks,
+                                   void* vq, void* vs, const int32_t* pos, const int32_t* prefix_len,
+                                   const void* cos_tbl, const void* sin_tbl, int n_pos, void* ao, int B, int H,
+                                   int Hkv, int D, int max_t, int max_p, void* stream) {
+  using namespace q40;
+  if (!qkv || !pk || !pv || !kq || !ks || !vq || !vs || !pos || !prefix_len || !cos_tbl || !sin_tbl || !ao)
+    return Q40_E_NULL;
+  if (D != 128) return Q40_E_UNSUPPORTED;
+  if (B < 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0 || max_t <= 0 || max_p <= 0 || n_pos <= 0) return Q40_E_SHAPE;
+  if (W < (int64_t)(H + 2 * Hkv) * 128 || W % 8 != 0) return Q40_E_SHAPE;
+  if (B == 0) return Q40_OK;
+  if (!q40_aligned(qkv, 16) || !q40_aligned(pk, 16) || !q40_aligned(pv, 16) || !q40_aligned(kq, 16) ||
+      !q40_aligned(vq, 16) || !q40_aligned(cos_tbl, 16) || !q40_aligned(sin_tbl, 16))
+    return Q40_E_ALIGN;
+  if ((int64_t)B * H * TF_CLUSTER > 0x7fffffffLL) return Q40_E_SHAPE;
+  TreeFusedArgs a{};
+  a.qkv = (__half*)qkv; a.W = W; a.pk = (const __half*)pk; a.pv = (const __half*)pv;
+  a.kq = (int8_t*)kq; a.ks = (__half*)ks; a.vq = (int8_t*)vq; a.vs = (__half*)vs;
+  a.pos = pos; a.prefix_len = prefix_len; a.cos_tbl = (const __half*)cos_tbl; a.sin_tbl = (const __half*)sin_tbl;
+  a.ao = (__half*)ao; a.H = H; a.Hkv = Hkv; a.max_t = max_t; a.max_p = max_p; a.n_pos = n_pos;
+  attn_tree_fused_kernel<<<(unsigned)(B * H * TF_CLUSTER), TF_THREADS, 0, (cudaStream_t)stream>>>(a);
+  Q40_LAUNCH_CHECK();
+  return Q40_OK;
+}

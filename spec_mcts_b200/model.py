@@ -215,6 +215,8 @@ class Transformer(nn.Module):
         self.use_megakernel = False
         # B <= 8: the fused matmuls read a rearranged ("tiled") copy of each weight, made on first use
         self.use_tiled = True
+        # width <= 16: rotary embedding, cache append and attention as one cluster launch
+        self.use_fused_attn = True
         self._layer_table = None
         self._trace = None       # optional int64 tensor [6 * n_layers + 8]: barrier timestamps of the step kernel
 
@@ -366,18 +368,27 @@ class Transformer(nn.Module):
             att, ff = layer.attention, layer.feed_forward
             self._fused(1, [att.wq, att.wk, att.wv], [q, k, v], W, h, p.dim, B,
                         norm_w=layer.attention_norm.weight, ss_in=ss_ffn, ss_in_count=c_ffn, st=st)
-            check(lib.q40_rope_kv_append(q.data_ptr(), W, k.data_ptr(), W, v.data_ptr(), W, pos.data_ptr(),
-                                         plen.data_ptr(), self._cos.data_ptr(), self._sin.data_ptr(), self._n_pos,
-                                         att.cache_k.data_ptr(), att.cache_k_s.data_ptr(),
-                                         att.cache_v.data_ptr(), att.cache_v_s.data_ptr(), B, H, Hkv, D,
-                                         p.max_seq_len, st), "q40_rope_kv_append")
-            pk, pv = att.cache_prompt_k, att.cache_prompt_v
-            check(lib.q40_attn_tree_decode(q.data_ptr(), W, pk.data_ptr(), pv.data_ptr(), p.max_prompt_seq_len,
-                                           plen.data_ptr(), pk.stride(0), pk.stride(1), att.cache_k.data_ptr(),
-                                           att.cache_k_s.data_ptr(), att.cache_v.data_ptr(),
-                                           att.cache_v_s.data_ptr(), p.max_seq_len, pos.data_ptr(), k.data_ptr(),
-                                           v.data_ptr(), W, ao.data_ptr(), B, H, Hkv, D, aws.data_ptr(),
-                                           aws.numel(), st), "q40_attn_tree_decode")
+            if self.use_fused_attn:
+                pk, pv = att.cache_prompt_k, att.cache_prompt_v
+                check(lib.q40_attn_tree_fused(qkv.data_ptr(), W, pk.data_ptr(), pv.data_ptr(), att.cache_k.data_ptr(),
+                                              att.cache_k_s.data_ptr(), att.cache_v.data_ptr(),
+                                              att.cache_v_s.data_ptr(), pos.data_ptr(), plen.data_ptr(),
+                                              self._cos.data_ptr(), self._sin.data_ptr(), self._n_pos, ao.data_ptr(),
+                                              B, H, Hkv, D, p.max_seq_len, p.max_prompt_seq_len, st),
+                      "q40_attn_tree_fused")
+            else:
+                check(lib.q40_rope_kv_append(q.data_ptr(), W, k.data_ptr(), W, v.data_ptr(), W, pos.data_ptr(),
+                                             plen.data_ptr(), self._cos.data_ptr(), self._sin.data_ptr(), self._n_pos,
+                                             att.cache_k.data_ptr(), att.cache_k_s.data_ptr(),
+                                             att.cache_v.data_ptr(), att.cache_v_s.data_ptr(), B, H, Hkv, D,
+                                             p.max_seq_len, st), "q40_rope_kv_append")
+                pk, pv = att.cache_prompt_k, att.cache_prompt_v
+                check(lib.q40_attn_tree_decode(q.data_ptr(), W, pk.data_ptr(), pv.data_ptr(), p.max_prompt_seq_len,
+                                               plen.data_ptr(), pk.stride(0), pk.stride(1), att.cache_k.data_ptr(),
+                                               att.cache_k_s.data_ptr(), att.cache_v.data_ptr(),
+                                               att.cache_v_s.data_ptr(), p.max_seq_len, pos.data_ptr(), k.data_ptr(),
+                                               v.data_ptr(), W, ao.data_ptr(), B, H, Hkv, D, aws.data_ptr(),
+                                               aws.numel(), st), "q40_attn_tree_decode")
             self._fused(2, [att.wo], [h], p.dim, ao, H * D, B, h_in=h, ldh=p.dim, ss_out=ss_attn,
                         ss_out_count=c_attn, st=st)
             self._fused(3, [ff.w1, ff.w3], [gbuf, gbuf], hid, h, p.dim, B, norm_w=layer.ffn_norm.weight,
@@ -515,11 +526,11 @@ class Transformer(nn.Module):
         buffers (`_tok_dev`, `_pos_dev`); returns the static logits buffer [B, vocab]."""
         fused = self.use_fused and B <= 16 and self.tp_world == 1
         mega = self.use_megakernel and B <= 8 and self.tp_world == 1
-        self.launches_per_step = 1 if mega else self.params.n_layers * (7 if fused else 13) + (2 if fused else 1)
+        self.launches_per_step = 1 if mega else self.params.n_layers * ((5 if self.use_fused_attn else 7) if fused else 13) + (2 if fused else 1)
         if not self.use_cuda_graph:
             return self._decode_body(B)
         key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster, self.use_megakernel,
-               self.use_tiled)
+               self.use_tiled, self.use_fused_attn)
         g = self._graphs.get(key)
         if g is None:
             # torch requires capture on a side stream after a warm-up run
@@ -534,7 +545,7 @@ class Transformer(nn.Module):
                     # this device cannot schedule 16-CTA clusters: use the portable size
                     self.max_cluster = 8
                     key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster,
-                           self.use_megakernel, self.use_tiled)
+                           self.use_megakernel, self.use_tiled, self.use_fused_attn)
                     self._decode_body(B)
             torch.cuda.current_stream(self.device).wait_stream(s)
             torch.cuda.synchronize(self.device)

@@ -412,3 +412,44 @@ def test_rope_kv_append_and_tree_decode(K):
         for b in range(B):
             hist_k[b].append(kd[b])
             hist_v[b].append(vd[b])
+
+
+def test_attn_tree_fused_matches_two_call_path(K):
+    """The single-launch small-width attention (rotary + append + attention per cluster) against
+    q40_rope_kv_append + q40_attn_tree_decode: identical cache bytes, outputs within fp32 merge order."""
+    from spec_mcts_b200._lib import check, lib
+    rng = np.random.default_rng(12)
+    B, H, Hkv, D, maxB, maxT, maxP, plen, n_pos = 5, 8, 4, 128, 6, 40, 300, 277, 400
+    W = (H + 2 * Hkv) * D
+    cos, sin = O.rope_tables(D, n_pos, 1e6)
+    cos_d, sin_d = dev(np.ascontiguousarray(cos[:, :64])), dev(np.ascontiguousarray(sin[:, :64]))
+    pk = dev(rng.standard_normal((maxP, Hkv, D)).astype(np.float16))
+    pv = dev(rng.standard_normal((maxP, Hkv, D)).astype(np.float16))
+    mk = lambda: (torch.zeros((maxB, maxT, Hkv, 64), dtype=torch.int8, device="cuda"),
+                  torch.zeros((maxB, maxT, Hkv, 2), dtype=torch.float16, device="cuda"))
+    (kq1, ks1), (vq1, vs1), (kq2, ks2), (vq2, vs2) = mk(), mk(), mk(), mk()
+    plen_d = torch.tensor([plen], dtype=torch.int32, device="cuda")
+    ws = torch.empty(lib.q40_attn_shared_prefix_workspace_bytes(B, H, D, maxP), dtype=torch.uint8, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    for step in range(35):
+        pos_d = torch.full((maxB,), plen + step, dtype=torch.int32, device="cuda")
+        qkv = dev(rng.standard_normal((B, W)).astype(np.float16))
+        a = qkv.clone()
+        q, k, v = a[:, :H * D], a[:, H * D:(H + Hkv) * D], a[:, (H + Hkv) * D:]
+        check(lib.q40_rope_kv_append(q.data_ptr(), W, k.data_ptr(), W, v.data_ptr(), W, pos_d.data_ptr(),
+                                     plen_d.data_ptr(), cos_d.data_ptr(), sin_d.data_ptr(), n_pos, kq1.data_ptr(),
+                                     ks1.data_ptr(), vq1.data_ptr(), vs1.data_ptr(), B, H, Hkv, D, maxT, st))
+        o1 = torch.empty((B, H * D), dtype=torch.float16, device="cuda")
+        check(lib.q40_attn_tree_decode(q.data_ptr(), W, pk.data_ptr(), pv.data_ptr(), maxP, plen_d.data_ptr(),
+                                       pk.stride(0), pk.stride(1), kq1.data_ptr(), ks1.data_ptr(), vq1.data_ptr(),
+                                       vs1.data_ptr(), maxT, pos_d.data_ptr(), k.data_ptr(), v.data_ptr(), W,
+                                       o1.data_ptr(), B, H, Hkv, D, ws.data_ptr(), ws.numel(), st))
+        o2 = torch.empty((B, H * D), dtype=torch.float16, device="cuda")
+        check(lib.q40_attn_tree_fused(qkv.data_ptr(), W, pk.data_ptr(), pv.data_ptr(), kq2.data_ptr(), ks2.data_ptr(),
+                                      vq2.data_ptr(), vs2.data_ptr(), pos_d.data_ptr(), plen_d.data_ptr(),
+                                      cos_d.data_ptr(), sin_d.data_ptr(), n_pos, o2.data_ptr(), B, H, Hkv, D, maxT,
+                                      maxP, st))
+        assert torch.equal(kq1, kq2) and torch.equal(vq1, vq2)
+        assert torch.equal(ks1.view(torch.int16), ks2.view(torch.int16))
+        assert torch.equal(vs1.view(torch.int16), vs2.view(torch.int16))
+        assert_close(host(o2), host(o1), rtol=1e-2, atol=2e-3)
