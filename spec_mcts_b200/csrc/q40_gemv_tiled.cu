@@ -400,7 +400,7 @@ extern "C" int q40_gemv_tiled(int mode, int nmat, const void* const* bw, const v
   if (mode < 0 || mode > 3 || nmat < 1 || nmat > 3) return Q40_E_UNSUPPORTED;
   if (mode == 3 && nmat != 2) return Q40_E_UNSUPPORTED;
   if (mode == 2 && nmat != 1) return Q40_E_UNSUPPORTED;
-  if (M < 1 || M > 8 || K < 16 || K % 16 != 0 || lda < K || lda % 8 != 0) return Q40_E_SHAPE;
+  if (M < 1 || M > 16 || K < 16 || K % 16 != 0 || lda < K || lda % 8 != 0) return Q40_E_SHAPE;
   if (!q40_aligned(a, 16)) return Q40_E_ALIGN;
   if ((mode == 1 || mode == 3) && (!norm_w || !ss_in || ss_in_count < 1 || !q40_aligned(norm_w, 16)))
     return Q40_E_NULL;
@@ -438,7 +438,7 @@ extern "C" int q40_gemv_tiled(int mode, int nmat, const void* const* bw, const v
   if (mode == 2 && ss_out_count != p.prob[0].nspans * nsplit * cluster_x) return Q40_E_SHAPE;
   cudaStream_t st = (cudaStream_t)stream;
   const bool pdl = use_pdl != 0;
-  const int mt = 1;
+  const int mt = (M <= 8) ? 1 : 2;
 #define Q40_TILED(MTV, PROV, EPIV) launch_tiled<MTV, PROV, EPIV>(p, grid_x, nsplit, cluster_x, st, pdl)
   if (mt == 1) {
     switch (mode) {
@@ -448,7 +448,12 @@ extern "C" int q40_gemv_tiled(int mode, int nmat, const void* const* bw, const v
       default: return Q40_TILED(1, PRO_NORM, EPI_SILU);
     }
   }
-  return Q40_E_UNSUPPORTED;
+  switch (mode) {
+    case 0: return Q40_TILED(2, PRO_NONE, EPI_STORE);
+    case 1: return Q40_TILED(2, PRO_NORM, EPI_STORE);
+    case 2: return Q40_TILED(2, PRO_NONE, EPI_RESIDUAL);
+    default: return Q40_TILED(2, PRO_NORM, EPI_SILU);
+  }
 #undef Q40_TILED
 }
 

@@ -213,10 +213,10 @@ class Transformer(nn.Module):
         self.max_cluster = 16
         # B <= 8 without tensor parallelism can run the whole step as one persistent kernel
         self.use_megakernel = False
-        # B <= 8: the fused matmuls read a rearranged ("tiled") copy of each weight, made on first use
+        # B <= 16: the fused matmuls read a rearranged ("tiled") copy of each weight, made on first use
         self.use_tiled = True
         # width <= 16: rotary embedding, cache append and attention as one cluster launch
-        self.use_fused_attn = True
+        self.use_fused_attn = False
         self._layer_table = None
         self._trace = None       # optional int64 tensor [6 * n_layers + 8]: barrier timestamps of the step kernel
 
@@ -325,7 +325,7 @@ class Transformer(nn.Module):
         import ctypes
         n = len(lins)
         P = ctypes.c_void_p * n
-        tiled = self.use_tiled and M <= 8 and all(l.kn()[1] % 256 == 0 and l.kn()[0] % 16 == 0 for l in lins)
+        tiled = self.use_tiled and M <= 16 and all(l.kn()[1] % 256 == 0 and l.kn()[0] % 16 == 0 for l in lins)
         if tiled:
             for l in lins:
                 if getattr(l, "_tiled", None) is None or l._tiled_src != l.w.data_ptr():

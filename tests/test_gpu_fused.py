@@ -56,7 +56,7 @@ def test_mode0_three_matrices(K, M, KN, cluster):
         close(o.cpu().numpy(), O.matmul_q40(a, q, s, (Kd, n)))
 
 
-@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("M", [1, 3, 8, 10, 16])
 @pytest.mark.parametrize("KN", [(512, 256), (4096, 4096), (4096, 11008), (11008, 4096), (1024, 768)])
 def test_tiled_mode0_and_relayout(K, M, KN):
     """The rearranged weight copy: mode 0 on tiled streams against the oracle and against the
@@ -85,8 +85,6 @@ def test_layer_chain_modes_1_2_3(K, M, dims, tiled):
     stage against the oracle computed from the GPU's own previous stage (so tolerances do not
     compound), with programmatic dependent launch on."""
     dim, hid = dims
-    if tiled and M > 8:
-        pytest.skip("the tiled kernels serve up to 8 rows")
     rng = np.random.default_rng(dim + M)
     sd = 0.5 / np.sqrt(dim / 256)
     wq, wk, wo = qmat(rng, dim, dim, sd), qmat(rng, dim, 256, sd), qmat(rng, dim, dim, sd)
