@@ -117,7 +117,8 @@ def test_layer_chain_modes_1_2_3(K, M, dims, tiled):
     g = K.gemv_fused(3, h2, [D(w1, (dim, hid)), D(w3, (dim, hid))], norm_w=dev(nw), ss_in=ss2, use_pdl=True, tiled=tiled)
     xn2 = O.rmsnorm(h2_np, nw, 1e-5)
     gref = O.silu_mul(O.matmul_q40(xn2, *w1, (dim, hid)), O.matmul_q40(xn2, *w3, (dim, hid)))
-    close(g.cpu().numpy(), gref, rtol=3e-2, atol=2e-2)
+    # a product of two matmul outputs: their tolerances add
+    close(g.cpu().numpy(), gref, rtol=3e-2, atol=8e-2)
     # mode 2 again (w2), in place
     g_np = g.cpu().numpy()
     h3, ss3 = K.gemv_fused(2, g, [D(w2, (hid, dim))], h_in=h2, use_pdl=True, tiled=tiled)
