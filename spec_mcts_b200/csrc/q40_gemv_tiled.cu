@@ -29,11 +29,12 @@ namespace cg = cooperative_groups;
 namespace q40 {
 namespace tiled {
 
-constexpr int FW = 4;                       // warps per CTA
+constexpr int FW = 8;                       // warps per CTA: warp w serves column group w & 3 and k slice w >> 2
+constexpr int KS = FW / 4;                  // k slices per CTA
 constexpr int FT = FW * 32;
-constexpr int F_DEPTH = 4;                  // ring slots (16-row steps) per warp
-constexpr int F_SLOT_W = 4 * 32 * 16;       // weights of one step: 4 groups x 32 lanes x 16 B
-constexpr int F_SLOT_BYTES = F_SLOT_W + 4 * 32 * 8;   // + 4 groups x 32 lanes x 8 B of scales (lane-private copies)
+constexpr int F_DEPTH = 4;                  // ring slots (16-row steps of one group) per warp
+constexpr int F_SLOT_W = 32 * 16;           // weights of one group-step: 32 lanes x 16 B (four 16x16 tiles)
+constexpr int F_SLOT_BYTES = F_SLOT_W + 32 * 8;   // + 32 lanes x 8 B of scales (lane-private copies)
 constexpr int T_STEP_BYTES = 2048 + 128;    // one step in the tiled stream: weights + 4 x 16 scales
 constexpr int F_SPAN_BYTES = 128;
 constexpr int F_SPAN_COLS = 256;
@@ -94,7 +95,7 @@ __device__ __forceinline__ void f_wait() { asm volatile("cp.async.wait_group %0;
 __device__ __forceinline__ int f_span_col(int span, int lc) { return span * F_SPAN_COLS + lc; }
 
 template <int MT, int PRO, int EPI>
-__global__ void __launch_bounds__(FT, (MT == 1 ? 3 : 2))
+__global__ void __launch_bounds__(FT, (MT == 1 ? 4 : 3))
 gemv_tiled_kernel(const TiledParams p) {
   extern __shared__ __align__(16) unsigned char smem[];
   cg::cluster_group cluster = cg::this_cluster();
@@ -123,23 +124,22 @@ gemv_tiled_kernel(const TiledParams p) {
   float* s_inv = reinterpret_cast<float*>(smem + FW * F_DEPTH * F_SLOT_BYTES + MT * 8 * xs_ld * 2);
   const uint32_t ring_u32 = (uint32_t)__cvta_generic_to_shared(ring) + warp * (F_DEPTH * F_SLOT_BYTES);
 
-  // tiled stream of this span: K/16 steps of T_STEP_BYTES; warp w owns steps (kb/16 + w), +FW, ...
+  // tiled stream of this span: K/16 steps of T_STEP_BYTES; this warp reads the part of column group
+  // gq4 of the steps (kb/16 + ksl), + KS, ...
+  const int gq4 = warp & 3, ksl = warp >> 2;
   const int ksteps_total = p.K / 16;
   const bool col_ok = span < pr.nspans;
-  const uint8_t* sbase = pr.bw + ((int64_t)span * ksteps_total + kb / 16 + warp) * T_STEP_BYTES;
+  const uint8_t* sbase = pr.bw + ((int64_t)span * ksteps_total + kb / 16 + ksl) * T_STEP_BYTES;
   auto issue = [&](int j, int slot) {      // j-th step of this warp
     const uint32_t base = ring_u32 + slot * F_SLOT_BYTES;
-    const uint8_t* sp = sbase + (int64_t)j * FW * T_STEP_BYTES;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      f_cp16(base + (q * 32 + lane) * 16, sp + (q * 32 + lane) * 16, col_ok);                 // weights of group q
-      f_cp8(base + F_SLOT_W + (q * 32 + lane) * 8, sp + 2048 + q * 32 + t * 8, col_ok);       // scales of k rows 4t..4t+3
-    }
+    const uint8_t* sp = sbase + (int64_t)j * KS * T_STEP_BYTES;
+    f_cp16(base + lane * 16, sp + (gq4 * 32 + lane) * 16, col_ok);                 // four tiles of the group
+    f_cp8(base + F_SLOT_W + lane * 8, sp + 2048 + gq4 * 32 + t * 8, col_ok);       // scales of k rows 4t..4t+3
   };
 
   // ---- prologue: weights only; nothing here depends on the previous kernel ----
-  // warp w owns steps w, w+FW, ...; its j-th step lives in ring slot j % DEPTH
-  const int my_steps = (nsteps > warp) ? (nsteps - warp + FW - 1) / FW : 0;
+  // its j-th step lives in ring slot j % DEPTH
+  const int my_steps = (nsteps > ksl) ? (nsteps - ksl + KS - 1) / KS : 0;
 #pragma unroll
   for (int j = 0; j < F_DEPTH; ++j) {
     if (j < my_steps) issue(j, j);
@@ -195,20 +195,18 @@ gemv_tiled_kernel(const TiledParams p) {
     __syncthreads();
   }
 
-  float acc[MT][16][4];
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-    for (int i = 0; i < 16; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) acc[mt][i][j] = 0.f;
-  float corr[MT][4][4];      // per 64-column group: sum over k of scale * x (every row of the tile the same)
+  float acc[MT][4][4];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) corr[mt][i][j] = 0.f;
+      for (int j = 0; j < 4; ++j) acc[mt][i][j] = 0.f;
+  float corr[MT][4];         // sum over k of scale * x for this group (every row of a tile the same)
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) corr[mt][j] = 0.f;
 
   // ---- main loop: consume the oldest slot, refill it with the step DEPTH ahead ----
   const __half* xlane = xs + g * xs_ld + 4 * t;
@@ -216,34 +214,29 @@ gemv_tiled_kernel(const TiledParams p) {
     f_wait<F_DEPTH - 1>();            // the oldest outstanding group (step j) has landed
     const int slot = j % F_DEPTH;
     const unsigned char* sb = ring + (warp * F_DEPTH + slot) * F_SLOT_BYTES;
-    const int step = warp + j * FW;
-    // activations of k rows 4t .. 4t+3 of this step for batch row g
-    uint2 xv[MT];
+    const int step = ksl + j * KS;
+    const uint4 w = *reinterpret_cast<const uint4*>(sb + lane * 16);
+    const uint2 sc = *reinterpret_cast<const uint2*>(sb + F_SLOT_W + lane * 8);
+    uint32_t yb[MT][2];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) xv[mt] = *reinterpret_cast<const uint2*>(xlane + step * 16 + mt * 8 * xs_ld);
+    for (int mt = 0; mt < MT; ++mt) {
+      // activations of k rows 4t .. 4t+3 of this step for batch row g, times their scales
+      const uint2 xv = *reinterpret_cast<const uint2*>(xlane + step * 16 + mt * 8 * xs_ld);
+      yb[mt][0] = h2_as_u32(__hmul2(u32_as_h2(xv.x), u32_as_h2(sc.x)));   // k rows 4t, 4t+1
+      yb[mt][1] = h2_as_u32(__hmul2(u32_as_h2(xv.y), u32_as_h2(sc.y)));   // k rows 4t+2, 4t+3
+      f_mma(corr[mt], 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, yb[mt][0], yb[mt][1]);
+    }
+    const uint32_t wds[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const uint4 w = *reinterpret_cast<const uint4*>(sb + (q * 32 + lane) * 16);
-      const uint2 sc = *reinterpret_cast<const uint2*>(sb + F_SLOT_W + (q * 32 + lane) * 8);
-      uint32_t yb[MT][2];
+    for (int jt = 0; jt < 4; ++jt) {
+      const uint32_t v = wds[jt];
+      // nibble -> fp16 value 72 + code: bits 4..7 of each 16-bit half under exponent 0x5400, sign bit flipped
+      const uint32_t a0 = lop3_and_xor(v, 0x00F000F0u, 0x54805480u);          // column g,   k 4t, 4t+1
+      const uint32_t a1 = lop3_and_xor(v << 4, 0x00F000F0u, 0x54805480u);     // column g+8, k 4t, 4t+1
+      const uint32_t a2 = lop3_and_xor(v >> 8, 0x00F000F0u, 0x54805480u);     // column g,   k 4t+2, 4t+3
+      const uint32_t a3 = lop3_and_xor(v >> 4, 0x00F000F0u, 0x54805480u);     // column g+8, k 4t+2, 4t+3
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        yb[mt][0] = h2_as_u32(__hmul2(u32_as_h2(xv[mt].x), u32_as_h2(sc.x)));   // scale * x, k rows 4t, 4t+1
-        yb[mt][1] = h2_as_u32(__hmul2(u32_as_h2(xv[mt].y), u32_as_h2(sc.y)));   // k rows 4t+2, 4t+3
-        f_mma(corr[mt][q], 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, yb[mt][0], yb[mt][1]);
-      }
-      const uint32_t wds[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-      for (int jt = 0; jt < 4; ++jt) {
-        const uint32_t v = wds[jt];
-        // nibble -> fp16 value 72 + code: bits 4..7 of each 16-bit half under exponent 0x5400, sign bit flipped
-        const uint32_t a0 = lop3_and_xor(v, 0x00F000F0u, 0x54805480u);          // column g,   k 4t, 4t+1
-        const uint32_t a1 = lop3_and_xor(v << 4, 0x00F000F0u, 0x54805480u);     // column g+8, k 4t, 4t+1
-        const uint32_t a2 = lop3_and_xor(v >> 8, 0x00F000F0u, 0x54805480u);     // column g,   k 4t+2, 4t+3
-        const uint32_t a3 = lop3_and_xor(v >> 4, 0x00F000F0u, 0x54805480u);     // column g+8, k 4t+2, 4t+3
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) f_mma(acc[mt][q * 4 + jt], a0, a1, a2, a3, yb[mt][0], yb[mt][1]);
-      }
+      for (int mt = 0; mt < MT; ++mt) f_mma(acc[mt][jt], a0, a1, a2, a3, yb[mt][0], yb[mt][1]);
     }
     // each lane reads back only what it copied itself and has consumed it by now, so the slot can
     // be refilled without a barrier
@@ -257,18 +250,18 @@ gemv_tiled_kernel(const TiledParams p) {
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-    for (int i = 0; i < 16; ++i)
+    for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) acc[mt][i][j] = fmaf(-72.0f, corr[mt][i >> 2][j], acc[mt][i][j]);
+      for (int j = 0; j < 4; ++j) acc[mt][i][j] = fmaf(-72.0f, corr[mt][j], acc[mt][i][j]);
 
   // ---- sum the warps: each stores its fragment slab, then the CTA partial is built per (m, column) ----
-  float4* slab = reinterpret_cast<float4*>(smem);                 // [FW][MT][16][32] float4
-  float* cta_part = reinterpret_cast<float*>(smem + FW * MT * 16 * 32 * 16);   // [M][256]
+  float4* slab = reinterpret_cast<float4*>(smem);                 // [FW][MT][4][32] float4
+  float* cta_part = reinterpret_cast<float*>(smem + FW * MT * 4 * 32 * 16);    // [M][256]
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-    for (int i = 0; i < 16; ++i)
-      slab[((warp * MT + mt) * 16 + i) * 32 + lane] =
+    for (int i = 0; i < 4; ++i)
+      slab[((warp * MT + mt) * 4 + i) * 32 + lane] =
           make_float4(acc[mt][i][0], acc[mt][i][1], acc[mt][i][2], acc[mt][i][3]);
   __syncthreads();
   {
@@ -277,13 +270,13 @@ gemv_tiled_kernel(const TiledParams p) {
     for (int idx = tid; idx < total; idx += FT) {
       const int m = idx / F_SPAN_COLS, lc = idx % F_SPAN_COLS;
       // column lc = 64*group + 16*tile + row; row r -> lane group r & 7, upper half of the tile if r >= 8
-      const int tile = lc >> 4, r = lc & 15;
+      const int grp = lc >> 6, jt = (lc >> 4) & 3, r = lc & 15;
       const int mt = m >> 3, mm = m & 7;
       const int fl = (r & 7) * 4 + (mm >> 1);
-      const int off = (((mt * 16 + tile) * 32 + fl) << 2) + (mm & 1) + 2 * (r >> 3);
+      const int off = (((mt * 4 + jt) * 32 + fl) << 2) + (mm & 1) + 2 * (r >> 3);
       float v = 0.f;
 #pragma unroll
-      for (int w = 0; w < FW; ++w) v += sl[off + w * (MT * 16 * 32 * 4)];
+      for (int ks = 0; ks < KS; ++ks) v += sl[off + (grp + 4 * ks) * (MT * 4 * 32 * 4)];   // the k slices of the group
       cta_part[idx] = v;
     }
   }
@@ -346,7 +339,7 @@ static int launch_tiled(const TiledParams& p, int grid_x, int nsplit, int cluste
   auto kern = gemv_tiled_kernel<MT, PRO, EPI>;
   const size_t ring = (size_t)FW * F_DEPTH * F_SLOT_BYTES;
   const size_t xs = (size_t)MT * 8 * (p.rows_per_split + F_XS_PAD) * 2 + 64 + (size_t)p.rows_per_split * 2;
-  const size_t red = (size_t)FW * MT * 16 * 32 * 16 + (size_t)p.M * F_SPAN_COLS * 4;
+  const size_t red = (size_t)FW * MT * 4 * 32 * 16 + (size_t)p.M * F_SPAN_COLS * 4;
   const size_t smem = (ring + xs) > red ? (ring + xs) : red;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
