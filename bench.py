@@ -164,6 +164,11 @@ def build_model(device):
         model.use_fused = os.environ["Q40_FUSED"] != "0"
     if "Q40_PDL" in os.environ:
         model.use_pdl = os.environ["Q40_PDL"] != "0"
+    if "Q40_FATTN" in os.environ:
+        model.fused_attn_max_width = int(os.environ["Q40_FATTN"])
+        model.use_fused_attn = model.fused_attn_max_width > 0
+    if "Q40_L2PF" in os.environ:
+        model.use_l2_prefetch = os.environ["Q40_L2PF"] != "0"
     if "Q40_CLUSTER" in os.environ:
         model.max_cluster = int(os.environ["Q40_CLUSTER"])
     return model
@@ -258,12 +263,13 @@ def gemv_roofline(model, width, reps):
 
     def one_pass():
         st = torch.cuda.current_stream(dev).cuda_stream
-        for grp in groups:
+        for gi, grp in enumerate(groups):
             k, n = grp[0].kn()
             if fused:
                 W = n * len(grp)
                 outs = [out[:, i * n:(i + 1) * n] for i in range(len(grp))]
-                model._fused(0, grp, outs, 3 * FFN, xs[k], k, width, st=st)
+                nxt = groups[gi + 1] if model.use_l2_prefetch and gi + 1 < len(groups) else ()
+                model._fused(0, grp, outs, 3 * FFN, xs[k], k, width, st=st, prefetch=nxt)
             else:
                 check(lib.q40_gemm_kn(xs[k].data_ptr(), k, grp[0].w.data_ptr(), grp[0].s.data_ptr(), out.data_ptr(),
                                       3 * FFN, width, n, k, 64, ws.data_ptr(), ws.numel(), st))

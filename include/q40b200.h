@@ -143,11 +143,17 @@ int q40_relayout_tiled(const void* bw, const void* bs, void* out, int N, int K, 
 
 /* q40_gemv_fused on tiled copies (same modes, arguments and results up to rounding: the scale is
  * applied to the activations, fp16(scale*x), instead of to the weight; 1 <= M <= 16; every
- * N % 256 == 0).  bw[i] are the tiled streams; bs is ignored and may be NULL. */
+ * N % 256 == 0).  bw[i] are the tiled streams; bs is ignored and may be NULL.
+ * prefetch[0..n_prefetch) (n_prefetch <= 3, host arrays read during the call; 16-byte aligned
+ * device ranges of prefetch_bytes[i] % 16 == 0 bytes) are requested into L2 while this launch
+ * runs: pass the weight streams of the launches that follow on the stream, so that HBM keeps
+ * streaming while those launches wait for their inputs.  The ranges are only hinted, never
+ * dereferenced by the SMs; n_prefetch = 0 turns the hint off. */
 int q40_gemv_tiled(int mode, int nmat, const void* const* bw, const void* const* bs, void* const* out,
                    const int* n_cols, int64_t ldc, const void* a, int64_t lda, int M, int K,
                    const void* norm_w, const float* ss_in, int ss_in_count, float eps, const void* h_in,
                    int64_t ldh, float* ss_out, int ss_out_count, int max_cluster, int use_pdl,
+                   const void* const* prefetch, const size_t* prefetch_bytes, int n_prefetch,
                    void* stream);
 int q40_gemv_tiled_ss_count(int N, int K, int max_cluster);
 
@@ -234,12 +240,15 @@ int q40_attn_tree_decode(const void* q, int64_t q_stride, const void* prefix_k, 
  * per (branch, head) splits the keys; no workspace): qkv [B, W] holds the new token's q heads, k
  * heads and v heads (un-rotated, W >= (H + 2 Hkv) * 128); the rotated key and the value are
  * appended to the Q4_0 suffix cache at slot (b, pos[b] - *prefix_len) and the attention output is
- * written to ao [B, H*128].  Caches and tables as in the two calls it replaces.
+ * written to ao [B, H*128].  Caches and tables as in the two calls it replaces.  use_pdl != 0
+ * launches with programmatic stream serialization: cached keys are fetched while the previous
+ * launch (the one that writes qkv) drains; pos, prefix_len and cache rows below pos must then
+ * have been complete before that previous launch started.
  * Replaces: the decode branch of Attention.forward (hf_model_q40_kv_shared.py:313-317, 330-405). */
 int q40_attn_tree_fused(void* qkv, int64_t W, const void* pk, const void* pv, void* kq, void* ks, void* vq,
                         void* vs, const int32_t* pos, const int32_t* prefix_len, const void* cos_tbl,
                         const void* sin_tbl, int n_pos, void* ao, int B, int H, int Hkv, int D, int max_t,
-                        int max_p, void* stream);
+                        int max_p, int use_pdl, void* stream);
 
 /* Rotary embedding of the new token's q [B, H*D] and k [B, Hkv*D] in place (position
  * pos_dev[b], tables cos/sin [n_pos, D/2] fp16) and Q4_0 append of the rotated k and of v to

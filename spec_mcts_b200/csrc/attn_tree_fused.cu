@@ -20,6 +20,7 @@ namespace q40 {
 
 constexpr int TF_THREADS = 256;
 constexpr int TF_CLUSTER = 8;
+constexpr int TF_KPG = 3;          // keys a group of 8 lanes holds in registers per batch (768 per cluster)
 
 struct TreeFusedArgs {
   __half* qkv;             // [B, W]: q heads, then k heads, then v heads of the new token (un-rotated)
@@ -36,30 +37,106 @@ struct TreeFusedArgs {
   const __half* sin_tbl;
   __half* ao;              // [B, H*128]
   int H, Hkv, max_t, max_p, n_pos;
+  void* trace;             // stage timestamps (trace builds only)
 };
 
-__global__ void __cluster_dims__(TF_CLUSTER, 1, 1) __launch_bounds__(TF_THREADS)
+// One cached key/value row as a lane fetched it: prompt rows are 2 x 16 B of K and of V (this lane's
+// 16 dims in fp16); suffix rows are 16 B of K codes, 16 B of V codes and the two scales.
+struct TfRaw { uint4 r[4]; };
+
+__device__ __forceinline__ void tf_load(const TreeFusedArgs& a, int key, int plen, int b, int hk, int sub, TfRaw& w) {
+  if (key < plen) {
+    const int64_t off = ((int64_t)key * a.Hkv + hk) * 128 + sub * 16;
+    w.r[0] = __ldg(reinterpret_cast<const uint4*>(a.pk + off));
+    w.r[1] = __ldg(reinterpret_cast<const uint4*>(a.pk + off + 8));
+    w.r[2] = __ldg(reinterpret_cast<const uint4*>(a.pv + off));
+    w.r[3] = __ldg(reinterpret_cast<const uint4*>(a.pv + off + 8));
+  } else {
+    const int64_t row = ((int64_t)b * a.max_t + (key - plen)) * a.Hkv + hk;
+    const int nib_lo = sub >> 2, boff = 16 * (sub & 3);
+    w.r[0] = __ldg(reinterpret_cast<const uint4*>(a.kq + row * 64 + boff));
+    w.r[1] = __ldg(reinterpret_cast<const uint4*>(a.vq + row * 64 + boff));
+    const uint32_t ksb = __half_as_ushort(__ldg(a.ks + row * 2 + nib_lo));
+    const uint32_t vsb = __half_as_ushort(__ldg(a.vs + row * 2 + nib_lo));
+    w.r[2].x = ksb | (vsb << 16);
+  }
+}
+__device__ __forceinline__ void tf_dec_half(const uint4& lo, const uint4& hi, float (&out)[16]) {
+  const __half2* a0 = reinterpret_cast<const __half2*>(&lo);
+  const __half2* a1 = reinterpret_cast<const __half2*>(&hi);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __half22float2(a0[i]); out[2 * i] = f.x; out[2 * i + 1] = f.y;
+    f = __half22float2(a1[i]); out[8 + 2 * i] = f.x; out[8 + 2 * i + 1] = f.y;
+  }
+}
+// the lane's 16 codes of a packed row (high nibbles for head dims 0..63, low for 64..127) times the scale
+__device__ __forceinline__ void tf_dec_q4(const uint4& bytes, uint32_t scale_bits, int nib_lo, float (&out)[16]) {
+  const __half2 sc = __half2half2(__ushort_as_half((unsigned short)scale_bits));
+  const uint32_t* wv = reinterpret_cast<const uint32_t*>(&bytes);
+#pragma unroll
+  for (int wi = 0; wi < 4; ++wi) {
+    const uint32_t c = nib_lo ? wv[wi] : (wv[wi] >> 4);
+    float2 f = __half22float2(__hmul2(codes_lo_to_h2(c), sc));
+    out[4 * wi] = f.x; out[4 * wi + 2] = f.y;
+    f = __half22float2(__hmul2(codes_lo_to_h2(c >> 8), sc));
+    out[4 * wi + 1] = f.x; out[4 * wi + 3] = f.y;
+  }
+}
+// merge the online-softmax states of lanes `delta` apart (both end up with the merged state)
+__device__ __forceinline__ void tf_merge_xor(float& m, float& l, float (&o)[16], int delta) {
+  const float m2 = __shfl_xor_sync(0xffffffffu, m, delta), l2 = __shfl_xor_sync(0xffffffffu, l, delta);
+  const float M = fmaxf(m, m2);
+  const float w1 = (m > -CUDART_INF_F) ? exp2f(m - M) : 0.f, w2 = (m2 > -CUDART_INF_F) ? exp2f(m2 - M) : 0.f;
+  l = l * w1 + l2 * w2;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float o2 = __shfl_xor_sync(0xffffffffu, o[i], delta);
+    o[i] = o[i] * w1 + o2 * w2;
+  }
+  m = M;
+}
+
+__global__ void __cluster_dims__(TF_CLUSTER, 1, 1) __launch_bounds__(TF_THREADS, 2)
 attn_tree_fused_kernel(const TreeFusedArgs a) {
   cg::cluster_group cluster = cg::this_cluster();
-  asm volatile("griddepcontrol.launch_dependents;");
-  __shared__ float at_m[32], at_l[32];
-  __shared__ __align__(16) float at_o[32 * 128];
-  __shared__ __align__(16) float at_part[132];
-  const int tid = threadIdx.x, lane = tid & 31;
-  const int cs = TF_CLUSTER;
+  Q40_TRACE_DECL
+  Q40_STAMP(0);
+  // phase 1 of the cluster barrier only says "this CTA is running" (waited for before the first
+  // store into a neighbour's shared memory); phase 2 publishes those stores
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  __shared__ float cta_m[8], cta_l[8];
+  __shared__ __align__(16) float cta_o[8 * 128];
+  __shared__ __align__(16) float recv[TF_CLUSTER][20];   // per source rank: 16 dims, max, sum
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int cs = TF_CLUSTER;
   const int rank = (int)cluster.block_rank();
   const int it = blockIdx.x / TF_CLUSTER;
   const int b = it / a.H, hq = it % a.H;
   const int rep = a.H / a.Hkv, hk = hq / rep;
   const int grp = tid >> 3, sub = tid & 7;
   const unsigned gmask = 0xffu << (lane & 24);
-  const int ngroups = 32 * cs;
+  constexpr int ngroups = 32 * cs;
   const int gidx = rank * 32 + grp;
   const float scale_log2 = (1.0f / sqrtf(128.0f)) * 1.4426950408889634f;
+  // positions and the prefix length were written before the previous launch started, and cache
+  // rows below `pos` by earlier decode steps: none of this waits for the previous launch
   const int plen = min(max(a.prefix_len[0], 0), a.max_p);
   int pos = a.pos[b];
   pos = min(max(pos, 0), a.n_pos - 1);
   const int slen = min(max(pos - plen, 0), a.max_t);
+  // keys: [0, plen) prompt (fp16), [plen, plen + slen) suffix (Q4_0), then the new token
+  const int total_keys = plen + slen + 1;
+  TfRaw raw[TF_KPG];
+#pragma unroll
+  for (int i = 0; i < TF_KPG; ++i) {
+    const int key = gidx + i * ngroups;
+    if (key < total_keys - 1) tf_load(a, key, plen, b, hk, sub, raw[i]);
+  }
+  Q40_STAMP(1);
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  Q40_STAMP(2);
 
   // this lane's 16 dims of the rotated, pre-scaled query and of the rotated new key; its 16 dims of v
   float qf[16];
@@ -95,68 +172,73 @@ attn_tree_fused_kernel(const TreeFusedArgs a) {
       qf[i] = __half2float(qr) * scale_log2;
     }
   }
-          float mx = -CUDART_INF_F, l = 0.f, o[16];
+  float mx = -CUDART_INF_F, l = 0.f, o[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) o[i] = 0.f;
-  // keys: [0, plen) prompt (fp16), [plen, plen + slen) suffix (Q4_0), then the new token
-  const int total_keys = plen + slen + 1;
-  for (int key = gidx; key < total_keys; key += ngroups) {
-    float kv_k[16], kv_v[16];
-    if (key < plen) {
-      const int64_t off = ((int64_t)key * a.Hkv + hk) * 128 + sub * 16;
-      const uint4 k0 = __ldg(reinterpret_cast<const uint4*>(a.pk + off));
-      const uint4 k1 = __ldg(reinterpret_cast<const uint4*>(a.pk + off + 8));
-      const uint4 v0 = __ldg(reinterpret_cast<const uint4*>(a.pv + off));
-      const uint4 v1 = __ldg(reinterpret_cast<const uint4*>(a.pv + off + 8));
-      const __half2* a0 = reinterpret_cast<const __half2*>(&k0);
-      const __half2* a1 = reinterpret_cast<const __half2*>(&k1);
-      const __half2* c0 = reinterpret_cast<const __half2*>(&v0);
-      const __half2* c1 = reinterpret_cast<const __half2*>(&v1);
+  const int nib_lo = sub >> 2;
+  Q40_STAMP_DEP(3, __half2float(kc[0]));
+  for (int base = 0; base < total_keys; base += TF_KPG * ngroups) {
+    if (base > 0) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float2 f = __half22float2(a0[i]); kv_k[2 * i] = f.x; kv_k[2 * i + 1] = f.y;
-        f = __half22float2(a1[i]); kv_k[8 + 2 * i] = f.x; kv_k[8 + 2 * i + 1] = f.y;
-        f = __half22float2(c0[i]); kv_v[2 * i] = f.x; kv_v[2 * i + 1] = f.y;
-        f = __half22float2(c1[i]); kv_v[8 + 2 * i] = f.x; kv_v[8 + 2 * i + 1] = f.y;
+      for (int i = 0; i < TF_KPG; ++i) {
+        const int key = base + gidx + i * ngroups;
+        if (key < total_keys - 1) tf_load(a, key, plen, b, hk, sub, raw[i]);
       }
-    } else if (key < plen + slen) {
-      const int64_t row = ((int64_t)b * a.max_t + (key - plen)) * a.Hkv + hk;
-      const int nib_lo = sub >> 2, boff = 16 * (sub & 3);
-      const uint4 kb4 = __ldg(reinterpret_cast<const uint4*>(a.kq + row * 64 + boff));
-      const uint4 vb4 = __ldg(reinterpret_cast<const uint4*>(a.vq + row * 64 + boff));
-      const __half2 ksc = __half2half2(a.ks[row * 2 + nib_lo]);
-      const __half2 vsc = __half2half2(a.vs[row * 2 + nib_lo]);
-      const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kb4);
-      const uint32_t* vw = reinterpret_cast<const uint32_t*>(&vb4);
-#pragma unroll
-      for (int wi = 0; wi < 4; ++wi) {
-        const uint32_t a = nib_lo ? kw[wi] : (kw[wi] >> 4);
-        const uint32_t c = nib_lo ? vw[wi] : (vw[wi] >> 4);
-        float2 f = __half22float2(__hmul2(codes_lo_to_h2(a), ksc));
-        kv_k[4 * wi] = f.x; kv_k[4 * wi + 2] = f.y;
-        f = __half22float2(__hmul2(codes_lo_to_h2(a >> 8), ksc));
-        kv_k[4 * wi + 1] = f.x; kv_k[4 * wi + 3] = f.y;
-        f = __half22float2(__hmul2(codes_lo_to_h2(c), vsc));
-        kv_v[4 * wi] = f.x; kv_v[4 * wi + 2] = f.y;
-        f = __half22float2(__hmul2(codes_lo_to_h2(c >> 8), vsc));
-        kv_v[4 * wi + 1] = f.x; kv_v[4 * wi + 3] = f.y;
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 16; ++i) { kv_k[i] = __half2float(kc[i]); kv_v[i] = __half2float(vc[i]); }
     }
-    float sdot = 0.f;
+    // the scores of the batch first (independent of one another), then one rescale of the state
+    float sd[TF_KPG];
+    float bm = -CUDART_INF_F;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) sdot = fmaf(qf[i], kv_k[i], sdot);
-    sdot += __shfl_xor_sync(gmask, sdot, 1);
-    sdot += __shfl_xor_sync(gmask, sdot, 2);
-    sdot += __shfl_xor_sync(gmask, sdot, 4);
-    const float mnew = fmaxf(mx, sdot);
-    const float corr = exp2f(mx - mnew), pw = exp2f(sdot - mnew);
-    l = l * corr + pw;
+    for (int i = 0; i < TF_KPG; ++i) {
+      const int key = base + gidx + i * ngroups;
+      sd[i] = -CUDART_INF_F;
+      if (key < total_keys) {
+        float kk[16];
+        if (key < plen) {
+          tf_dec_half(raw[i].r[0], raw[i].r[1], kk);
+        } else if (key < total_keys - 1) {
+          tf_dec_q4(raw[i].r[0], raw[i].r[2].x & 0xFFFFu, nib_lo, kk);
+        } else {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) o[i] = fmaf(pw, kv_v[i], o[i] * corr);
-    mx = mnew;
+          for (int d = 0; d < 16; ++d) kk[d] = __half2float(kc[d]);
+        }
+        float sdot = 0.f;
+#pragma unroll
+        for (int d = 0; d < 16; ++d) sdot = fmaf(qf[d], kk[d], sdot);
+        sdot += __shfl_xor_sync(gmask, sdot, 1);
+        sdot += __shfl_xor_sync(gmask, sdot, 2);
+        sdot += __shfl_xor_sync(gmask, sdot, 4);
+        sd[i] = sdot;
+        bm = fmaxf(bm, sdot);
+      }
+    }
+    if (base + gidx < total_keys) {          // the group has at least one key in this batch
+      const float mnew = fmaxf(mx, bm);
+      const float corr = (mx > -CUDART_INF_F) ? exp2f(mx - mnew) : 0.f;
+      l *= corr;
+#pragma unroll
+      for (int d = 0; d < 16; ++d) o[d] *= corr;
+#pragma unroll
+      for (int i = 0; i < TF_KPG; ++i) {
+        const int key = base + gidx + i * ngroups;
+        if (key < total_keys) {
+          float vv[16];
+          if (key < plen) {
+            tf_dec_half(raw[i].r[2], raw[i].r[3], vv);
+          } else if (key < total_keys - 1) {
+            tf_dec_q4(raw[i].r[1], raw[i].r[2].x >> 16, nib_lo, vv);
+          } else {
+#pragma unroll
+            for (int d = 0; d < 16; ++d) vv[d] = __half2float(vc[d]);
+          }
+          const float pw = exp2f(sd[i] - mnew);
+          l += pw;
+#pragma unroll
+          for (int d = 0; d < 16; ++d) o[d] = fmaf(pw, vv[d], o[d]);
+        }
+      }
+      mx = mnew;
+    }
   }
   // Q4_0 append of the new token's rotated key and its value: the first query head of a kv
   // group, rank 0, key group 0 (the 8 lanes hold the whole 128-dim row)
@@ -195,52 +277,57 @@ attn_tree_fused_kernel(const TreeFusedArgs a) {
     if (sub == 4) { a.ks[row * 2 + 1] = sk; a.vs[row * 2 + 1] = sv; }
   }
 
-          if (sub == 0) { at_m[grp] = mx; at_l[grp] = l; }
+  Q40_STAMP_DEP(4, mx);
+  // ---- the four key groups of a warp through shuffles, the eight warps through shared memory ----
+  tf_merge_xor(mx, l, o, 8);
+  tf_merge_xor(mx, l, o, 16);
+  if (lane < 8) {
+    if (lane == 0) { cta_m[warp] = mx; cta_l[warp] = l; }
 #pragma unroll
-  for (int i = 0; i < 16; i += 4)
-    *reinterpret_cast<float4*>(&at_o[grp * 128 + sub * 16 + i]) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+    for (int i = 0; i < 16; i += 4)
+      *reinterpret_cast<float4*>(&cta_o[warp * 128 + lane * 16 + i]) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+  }
   __syncthreads();
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");     // every CTA of the cluster is running
+  constexpr int per = 128 / cs;          // output dims finished by one rank
   if (tid < 128) {
     float Mx = -CUDART_INF_F;
-    for (int q = 0; q < 32; ++q) Mx = fmaxf(Mx, at_m[q]);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) Mx = fmaxf(Mx, cta_m[q]);
     float Ls = 0.f, acc = 0.f;
-    if (Mx > -CUDART_INF_F)
-      for (int q = 0; q < 32; ++q) {
-        const float w = exp2f(at_m[q] - Mx);
-        Ls = fmaf(at_l[q], w, Ls);
-        acc = fmaf(at_o[q * 128 + tid], w, acc);
-      }
-    at_part[2 + tid] = acc;
-    if (tid == 0) { at_part[0] = Mx; at_part[1] = Ls; }
-  }
-  cluster.sync();
-  {
-    // rank r finishes dims [r*per, (r+1)*per)
-    const int per = 128 / cs;
-    if (tid < per) {
-      const int d = rank * per + tid;
-      float pm[16], pl[16], po[16];
+    if (Mx > -CUDART_INF_F) {
 #pragma unroll
-      for (int r = 0; r < 16; ++r) {
-        if (r < cs) {
-          const float* rp = cluster.map_shared_rank(at_part, r);
-          pm[r] = rp[0]; pl[r] = rp[1]; po[r] = rp[2 + d];
-        } else { pm[r] = -CUDART_INF_F; pl[r] = 0.f; po[r] = 0.f; }
+      for (int q = 0; q < 8; ++q) {
+        const float w = exp2f(cta_m[q] - Mx);
+        Ls = fmaf(cta_l[q], w, Ls);
+        acc = fmaf(cta_o[q * 128 + tid], w, acc);
       }
-      float Mx = -CUDART_INF_F;
-#pragma unroll
-      for (int r = 0; r < 16; ++r) Mx = fmaxf(Mx, pm[r]);
-      float Ls = 0.f, acc = 0.f;
-#pragma unroll
-      for (int r = 0; r < 16; ++r) {
-        const float w = (pm[r] > -CUDART_INF_F) ? exp2f(pm[r] - Mx) : 0.f;
-        Ls = fmaf(pl[r], w, Ls);
-        acc = fmaf(po[r], w, acc);
-      }
-      a.ao[(int64_t)b * (a.H * 128) + hq * 128 + d] = __float2half_rn(Ls > 0.f ? acc / Ls : 0.f);
     }
+    // hand the CTA's partial to the rank that finishes this dim
+    float* dst = cluster.map_shared_rank(&recv[rank][0], tid / per);
+    dst[tid % per] = acc;
+    if (tid % per == 0) { dst[16] = Mx; dst[17] = Ls; }
   }
-  cluster.sync();   // nobody leaves while a neighbour may still read its partial
+  Q40_STAMP(5);
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  Q40_STAMP(6);
+  if (tid < per) {
+    float Mx = -CUDART_INF_F;
+#pragma unroll
+    for (int r = 0; r < cs; ++r) Mx = fmaxf(Mx, recv[r][16]);
+    float Ls = 0.f, acc = 0.f;
+#pragma unroll
+    for (int r = 0; r < cs; ++r) {
+      const float pm = recv[r][16];
+      const float w = (pm > -CUDART_INF_F) ? exp2f(pm - Mx) : 0.f;
+      Ls = fmaf(recv[r][17], w, Ls);
+      acc = fmaf(recv[r][tid], w, acc);
+    }
+    a.ao[(int64_t)b * (a.H * 128) + hq * 128 + rank * per + tid] = __float2half_rn(Ls > 0.f ? acc / Ls : 0.f);
+  }
+  Q40_STAMP(7);
+  Q40_TRACE_FLUSH(a.trace, 200);
 }
 
 }  // namespace q40
@@ -248,7 +335,7 @@ attn_tree_fused_kernel(const TreeFusedArgs a) {
 extern "C" int q40_attn_tree_fused(void* qkv, int64_t W, const void* pk, const void* pv, void* kq, void* ks,
                                    void* vq, void* vs, const int32_t* pos, const int32_t* prefix_len,
                                    const void* cos_tbl, const void* sin_tbl, int n_pos, void* ao, int B, int H,
-                                   int Hkv, int D, int max_t, int max_p, void* stream) {
+                                   int Hkv, int D, int max_t, int max_p, int use_pdl, void* stream) {
   using namespace q40;
   if (!qkv || !pk || !pv || !kq || !ks || !vq || !vs || !pos || !prefix_len || !cos_tbl || !sin_tbl || !ao)
     return Q40_E_NULL;
@@ -264,8 +351,23 @@ extern "C" int q40_attn_tree_fused(void* qkv, int64_t W, const void* pk, const v
   a.qkv = (__half*)qkv; a.W = W; a.pk = (const __half*)pk; a.pv = (const __half*)pv;
   a.kq = (int8_t*)kq; a.ks = (__half*)ks; a.vq = (int8_t*)vq; a.vs = (__half*)vs;
   a.pos = pos; a.prefix_len = prefix_len; a.cos_tbl = (const __half*)cos_tbl; a.sin_tbl = (const __half*)sin_tbl;
+#ifdef Q40_TRACE
+  a.trace = q40_trace_ptr;
+#endif
   a.ao = (__half*)ao; a.H = H; a.Hkv = Hkv; a.max_t = max_t; a.max_p = max_p; a.n_pos = n_pos;
-  attn_tree_fused_kernel<<<(unsigned)(B * H * TF_CLUSTER), TF_THREADS, 0, (cudaStream_t)stream>>>(a);
-  Q40_LAUNCH_CHECK();
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)(B * H * TF_CLUSTER), 1, 1);
+  cfg.blockDim = dim3(TF_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl ? 1 : 0;
+  cudaError_t e = cudaFuncSetAttribute(attn_tree_fused_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaLaunchKernelEx(&cfg, attn_tree_fused_kernel, a);
+  if (e != cudaSuccess) return (int)e;
   return Q40_OK;
 }

@@ -16,3 +16,8 @@ extern "C" const char* q40_strerror(int status) {
   if (status > 0) return cudaGetErrorString((cudaError_t)status);
   return "q40: unknown status";
 }
+
+#ifdef Q40_TRACE
+void* q40_trace_ptr = nullptr;
+extern "C" void q40_debug_trace(void* buf) { q40_trace_ptr = buf; }
+#endif

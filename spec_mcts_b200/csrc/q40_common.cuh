@@ -18,6 +18,37 @@
 
 static inline bool q40_aligned(const void* p, size_t a) { return ((uintptr_t)p % a) == 0; }
 
+// Optional stage timestamps (builds with -DQ40_TRACE only; compiled out otherwise): thread 0 of a CTA
+// reads the global nanosecond timer at up to 8 points and appends one record of 10 words
+// {kind, linear CTA id, t0..t7} to the buffer given to q40_debug_trace (word 0 = record counter,
+// word 1 = capacity in records, records from word 16).
+#ifdef Q40_TRACE
+extern void* q40_trace_ptr;
+#define Q40_TRACE_DECL unsigned long long q40_ts_[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define Q40_STAMP(i) \
+  do { if (threadIdx.x == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(q40_ts_[i])::"memory"); } while (0)
+#define Q40_STAMP_DEP(i, v) /* not before the float v is available */ \
+  do { if (threadIdx.x == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(q40_ts_[i]) : "f"(v) : "memory"); } while (0)
+#define Q40_TRACE_FLUSH(buf, kind)                                                                   \
+  do {                                                                                               \
+    unsigned long long* tb_ = (unsigned long long*)(buf);                                            \
+    if (threadIdx.x == 0 && tb_) {                                                                   \
+      const unsigned long long slot_ = atomicAdd(tb_, 1ull);                                         \
+      if (slot_ < tb_[1]) {                                                                          \
+        unsigned long long* r_ = tb_ + 16 + slot_ * 10;                                              \
+        r_[0] = (kind);                                                                              \
+        r_[1] = (unsigned long long)blockIdx.x + (unsigned long long)gridDim.x * blockIdx.y;         \
+        for (int i_ = 0; i_ < 8; ++i_) r_[2 + i_] = q40_ts_[i_];                                     \
+      }                                                                                              \
+    }                                                                                                \
+  } while (0)
+#else
+#define Q40_TRACE_DECL
+#define Q40_STAMP(i) do { } while (0)
+#define Q40_STAMP_DEP(i, v) do { } while (0)
+#define Q40_TRACE_FLUSH(buf, kind) do { } while (0)
+#endif
+
 namespace q40 {
 
 __device__ __forceinline__ uint32_t lop3_and_xor(uint32_t a, uint32_t mask, uint32_t x) {

@@ -29,16 +29,19 @@ namespace cg = cooperative_groups;
 namespace q40 {
 namespace tiled {
 
-constexpr int FW = 8;                       // warps per CTA: warp w serves column group w & 3 and k slice w >> 2
-constexpr int KS = FW / 4;                  // k slices per CTA
-constexpr int FT = FW * 32;
-constexpr int F_DEPTH = 4;                  // ring slots (16-row steps of one group) per warp
-constexpr int F_SLOT_W = 32 * 16;           // weights of one group-step: 32 lanes x 16 B (four 16x16 tiles)
-constexpr int F_SLOT_BYTES = F_SLOT_W + 32 * 8;   // + 32 lanes x 8 B of scales (lane-private copies)
+// Work split inside a CTA, chosen per batch width: a warp serves NG of the span's four 64-column
+// groups and one of KS interleaved k slices, so a CTA has (4 / NG) * KS warps.  NG = 4, KS = 4 (four
+// warps, 64 accumulator registers per 8 batch rows) measured fastest for up to 8 rows; NG = 2, KS = 2
+// (four warps, two of them per k slice) for 9..16 rows; eight-warp splits (NG = 1 or 2 with KS = 2 or 4)
+// were slower at every width.
+constexpr int F_DEPTH = 4;                  // ring slots (16-row steps) per warp
+constexpr int F_GROUP_W = 32 * 16;          // weights of one group-step: 32 lanes x 16 B (four 16x16 tiles)
+constexpr int F_GROUP_BYTES = F_GROUP_W + 32 * 8;   // + 32 lanes x 8 B of scales (lane-private copies)
 constexpr int T_STEP_BYTES = 2048 + 128;    // one step in the tiled stream: weights + 4 x 16 scales
 constexpr int F_SPAN_BYTES = 128;
 constexpr int F_SPAN_COLS = 256;
 constexpr int F_XS_PAD = 16;
+constexpr int PF_CHUNK = 4096;              // bytes per L2 prefetch request
 
 enum { PRO_NONE = 0, PRO_NORM = 1 };
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2 };
@@ -66,6 +69,11 @@ struct TiledParams {
   int64_t ldh;
   float* ss_out;
   int ss_out_count;
+  // weight streams a later launch will read: requested into L2 while this launch runs
+  const uint8_t* pf[3];
+  uint32_t pf_bytes[3];
+  void* trace;             // stage timestamps (trace builds only)
+  int recv_off;            // byte offset of the receive buffer in dynamic shared memory
 };
 
 __device__ __forceinline__ void f_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -94,13 +102,26 @@ __device__ __forceinline__ void f_wait() { asm volatile("cp.async.wait_group %0;
 
 __device__ __forceinline__ int f_span_col(int span, int lc) { return span * F_SPAN_COLS + lc; }
 
-template <int MT, int PRO, int EPI>
-__global__ void __launch_bounds__(FT, (MT == 1 ? 4 : 3))
+template <int MT, int NG, int KS, int PRO, int EPI>
+__global__ void __launch_bounds__((4 / NG) * KS * 32, (NG == 4 ? (MT == 1 ? 3 : 2) : (MT == 1 ? 4 : 3)))
 gemv_tiled_kernel(const TiledParams p) {
+  constexpr int NGW = 4 / NG;                // warps that share a k slice
+  constexpr int FW = NGW * KS;               // warps per CTA
+  constexpr int FT = FW * 32;
+  constexpr int F_SLOT_BYTES = NG * F_GROUP_BYTES;
+  constexpr int NT = NG * 4;                 // 16x16 tiles per warp and step
   extern __shared__ __align__(16) unsigned char smem[];
   cg::cluster_group cluster = cg::this_cluster();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
+  Q40_TRACE_DECL
+  Q40_STAMP(0);
+  // phase 1 of the cluster barrier only says "this CTA is running" (waited for before the first
+  // store into a neighbour's shared memory); phase 2 publishes those stores
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  const int nranks = (int)cluster.num_blocks();
+  const int rank = (int)cluster.block_rank();
+  const int slice = F_SPAN_COLS / nranks;            // 16, 32, 64, 128 or 256 columns finished by this rank
 
   // ---- which matrix and which 128-byte span of its rows ----
   int pi = 0, span = blockIdx.x;
@@ -123,18 +144,25 @@ gemv_tiled_kernel(const TiledParams p) {
   __half* xs = reinterpret_cast<__half*>(smem + FW * F_DEPTH * F_SLOT_BYTES);
   float* s_inv = reinterpret_cast<float*>(smem + FW * F_DEPTH * F_SLOT_BYTES + MT * 8 * xs_ld * 2);
   const uint32_t ring_u32 = (uint32_t)__cvta_generic_to_shared(ring) + warp * (F_DEPTH * F_SLOT_BYTES);
+  // [recv: nranks x M x slice floats] partial sums pushed by the cluster; a region of its own, because
+  // neighbours may push while this CTA is still in its main loop
+  float* recv = reinterpret_cast<float*>(smem + p.recv_off);
 
-  // tiled stream of this span: K/16 steps of T_STEP_BYTES; this warp reads the part of column group
-  // gq4 of the steps (kb/16 + ksl), + KS, ...
-  const int gq4 = warp & 3, ksl = warp >> 2;
+  // tiled stream of this span: K/16 steps of T_STEP_BYTES; this warp reads the part of column groups
+  // gq0 .. gq0 + NG - 1 of the steps (kb/16 + ksl), + KS, ...
+  const int gq0 = (warp % NGW) * NG, ksl = warp / NGW;
   const int ksteps_total = p.K / 16;
   const bool col_ok = span < pr.nspans;
   const uint8_t* sbase = pr.bw + ((int64_t)span * ksteps_total + kb / 16 + ksl) * T_STEP_BYTES;
   auto issue = [&](int j, int slot) {      // j-th step of this warp
     const uint32_t base = ring_u32 + slot * F_SLOT_BYTES;
     const uint8_t* sp = sbase + (int64_t)j * KS * T_STEP_BYTES;
-    f_cp16(base + lane * 16, sp + (gq4 * 32 + lane) * 16, col_ok);                 // four tiles of the group
-    f_cp8(base + F_SLOT_W + lane * 8, sp + 2048 + gq4 * 32 + t * 8, col_ok);       // scales of k rows 4t..4t+3
+#pragma unroll
+    for (int q = 0; q < NG; ++q) {
+      f_cp16(base + q * F_GROUP_BYTES + lane * 16, sp + ((gq0 + q) * 32 + lane) * 16, col_ok);   // four tiles of the group
+      f_cp8(base + q * F_GROUP_BYTES + F_GROUP_W + lane * 8, sp + 2048 + (gq0 + q) * 32 + t * 8,
+            col_ok);                                                                            // scales of k rows 4t..4t+3
+    }
   };
 
   // ---- prologue: weights only; nothing here depends on the previous kernel ----
@@ -145,8 +173,29 @@ gemv_tiled_kernel(const TiledParams p) {
     if (j < my_steps) issue(j, j);
     f_commit();
   }
+  // ---- ask L2 for the weight streams of the launches that follow (fire and forget): the dependent
+  // launches cannot start their own loads early enough to keep HBM busy across the hand-over ----
+  if (warp == FW - 1) {
+    const uint32_t ncta = gridDim.x * gridDim.y, cta = blockIdx.y * gridDim.x + blockIdx.x;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      const uint32_t bytes = p.pf_bytes[i];
+      const uint32_t nchunks = (bytes + PF_CHUNK - 1) / PF_CHUNK;
+      for (uint32_t c = cta * 32 + lane; c < nchunks; c += ncta * 32) {
+        const uint32_t off = c * PF_CHUNK;
+        const uint32_t sz = min((uint32_t)PF_CHUNK, bytes - off);     // a multiple of 16 (checked by the host)
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.pf[i] + off), "r"(sz) : "memory");
+      }
+    }
+  }
+  Q40_STAMP(1);
   asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  Q40_STAMP(2);
+  // the residual value of the first output this thread finishes, fetched now instead of at the very end
+  __half h_first = __float2half(0.f);
+  if (EPI == EPI_RESIDUAL && warp < p.M && lane < slice && col_ok)
+    h_first = p.h_in[(int64_t)warp * p.ldh + f_span_col(span, rank * slice + lane)];
 
   // ---- activations of this k range: raw copy first (and the norm weights), so that the loads do
   // not wait for the row statistics; then, for the RMSNorm prologue, normalise in place ----
@@ -168,8 +217,19 @@ gemv_tiled_kernel(const TiledParams p) {
         *reinterpret_cast<uint4*>(wn + idx * 8) = v;
       }
       for (int m = warp; m < p.M; m += FW) {
+        // all loads in flight before the first add (the partials sit in L2)
         float s = 0.f;
-        for (int i = lane; i < p.ss_in_count; i += 32) s += p.ss_in[(int64_t)m * p.ss_in_count + i];
+        const float* sp = p.ss_in + (int64_t)m * p.ss_in_count;
+        for (int i0 = 0; i0 < p.ss_in_count; i0 += 256) {
+          float part[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * 32 + lane;
+            part[u] = (i < p.ss_in_count) ? __ldcg(sp + i) : 0.f;
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) s += part[u];
+        }
         s = warp_sum(s);
         if (lane == 0) s_inv[m] = rsqrtf(s / (float)p.K + p.eps);
       }
@@ -195,18 +255,21 @@ gemv_tiled_kernel(const TiledParams p) {
     __syncthreads();
   }
 
-  float acc[MT][4][4];
+  Q40_STAMP(3);
+  float acc[MT][NT][4];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < NT; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[mt][i][j] = 0.f;
-  float corr[MT][4];         // sum over k of scale * x for this group (every row of a tile the same)
+  float corr[MT][NG][4];     // per 64-column group: sum over k of scale * x (every row of a tile the same)
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) corr[mt][j] = 0.f;
+    for (int q = 0; q < NG; ++q)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) corr[mt][q][j] = 0.f;
 
   // ---- main loop: consume the oldest slot, refill it with the step DEPTH ahead ----
   const __half* xlane = xs + g * xs_ld + 4 * t;
@@ -215,28 +278,33 @@ gemv_tiled_kernel(const TiledParams p) {
     const int slot = j % F_DEPTH;
     const unsigned char* sb = ring + (warp * F_DEPTH + slot) * F_SLOT_BYTES;
     const int step = ksl + j * KS;
-    const uint4 w = *reinterpret_cast<const uint4*>(sb + lane * 16);
-    const uint2 sc = *reinterpret_cast<const uint2*>(sb + F_SLOT_W + lane * 8);
-    uint32_t yb[MT][2];
+    // activations of k rows 4t .. 4t+3 of this step for batch row g
+    uint2 xv[MT];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      // activations of k rows 4t .. 4t+3 of this step for batch row g, times their scales
-      const uint2 xv = *reinterpret_cast<const uint2*>(xlane + step * 16 + mt * 8 * xs_ld);
-      yb[mt][0] = h2_as_u32(__hmul2(u32_as_h2(xv.x), u32_as_h2(sc.x)));   // k rows 4t, 4t+1
-      yb[mt][1] = h2_as_u32(__hmul2(u32_as_h2(xv.y), u32_as_h2(sc.y)));   // k rows 4t+2, 4t+3
-      f_mma(corr[mt], 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, yb[mt][0], yb[mt][1]);
-    }
-    const uint32_t wds[4] = {w.x, w.y, w.z, w.w};
+    for (int mt = 0; mt < MT; ++mt) xv[mt] = *reinterpret_cast<const uint2*>(xlane + step * 16 + mt * 8 * xs_ld);
 #pragma unroll
-    for (int jt = 0; jt < 4; ++jt) {
-      const uint32_t v = wds[jt];
-      // nibble -> fp16 value 72 + code: bits 4..7 of each 16-bit half under exponent 0x5400, sign bit flipped
-      const uint32_t a0 = lop3_and_xor(v, 0x00F000F0u, 0x54805480u);          // column g,   k 4t, 4t+1
-      const uint32_t a1 = lop3_and_xor(v << 4, 0x00F000F0u, 0x54805480u);     // column g+8, k 4t, 4t+1
-      const uint32_t a2 = lop3_and_xor(v >> 8, 0x00F000F0u, 0x54805480u);     // column g,   k 4t+2, 4t+3
-      const uint32_t a3 = lop3_and_xor(v >> 4, 0x00F000F0u, 0x54805480u);     // column g+8, k 4t+2, 4t+3
+    for (int q = 0; q < NG; ++q) {
+      const uint4 w = *reinterpret_cast<const uint4*>(sb + q * F_GROUP_BYTES + lane * 16);
+      const uint2 sc = *reinterpret_cast<const uint2*>(sb + q * F_GROUP_BYTES + F_GROUP_W + lane * 8);
+      uint32_t yb[MT][2];
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) f_mma(acc[mt][jt], a0, a1, a2, a3, yb[mt][0], yb[mt][1]);
+      for (int mt = 0; mt < MT; ++mt) {
+        yb[mt][0] = h2_as_u32(__hmul2(u32_as_h2(xv[mt].x), u32_as_h2(sc.x)));   // scale * x, k rows 4t, 4t+1
+        yb[mt][1] = h2_as_u32(__hmul2(u32_as_h2(xv[mt].y), u32_as_h2(sc.y)));   // k rows 4t+2, 4t+3
+        f_mma(corr[mt][q], 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, yb[mt][0], yb[mt][1]);
+      }
+      const uint32_t wds[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int jt = 0; jt < 4; ++jt) {
+        const uint32_t v = wds[jt];
+        // nibble -> fp16 value 72 + code: bits 4..7 of each 16-bit half under exponent 0x5400, sign bit flipped
+        const uint32_t a0 = lop3_and_xor(v, 0x00F000F0u, 0x54805480u);          // column g,   k 4t, 4t+1
+        const uint32_t a1 = lop3_and_xor(v << 4, 0x00F000F0u, 0x54805480u);     // column g+8, k 4t, 4t+1
+        const uint32_t a2 = lop3_and_xor(v >> 8, 0x00F000F0u, 0x54805480u);     // column g,   k 4t+2, 4t+3
+        const uint32_t a3 = lop3_and_xor(v >> 4, 0x00F000F0u, 0x54805480u);     // column g+8, k 4t+2, 4t+3
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) f_mma(acc[mt][q * 4 + jt], a0, a1, a2, a3, yb[mt][0], yb[mt][1]);
+      }
     }
     // each lane reads back only what it copied itself and has consumed it by now, so the slot can
     // be refilled without a barrier
@@ -245,25 +313,28 @@ gemv_tiled_kernel(const TiledParams p) {
   }
   f_wait<0>();
   __syncthreads();   // every warp is done with its ring slots and with xs
+  Q40_STAMP(4);
 
   // remove the constant 72 carried by every weight operand: acc -= 72 * sum_k(scale * x)
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < NT; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) acc[mt][i][j] = fmaf(-72.0f, corr[mt][j], acc[mt][i][j]);
+      for (int j = 0; j < 4; ++j) acc[mt][i][j] = fmaf(-72.0f, corr[mt][i >> 2][j], acc[mt][i][j]);
 
-  // ---- sum the warps: each stores its fragment slab, then the CTA partial is built per (m, column) ----
-  float4* slab = reinterpret_cast<float4*>(smem);                 // [FW][MT][4][32] float4
-  float* cta_part = reinterpret_cast<float*>(smem + FW * MT * 4 * 32 * 16);    // [M][256]
+  // ---- sum the warps: each stores its fragment slab; then every (m, column) sum of the CTA is pushed
+  // into the shared memory of the cluster rank that finishes that column ----
+  float4* slab = reinterpret_cast<float4*>(smem);                 // [FW][MT][NT][32] float4
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-      slab[((warp * MT + mt) * 4 + i) * 32 + lane] =
+    for (int i = 0; i < NT; ++i)
+      slab[((warp * MT + mt) * NT + i) * 32 + lane] =
           make_float4(acc[mt][i][0], acc[mt][i][1], acc[mt][i][2], acc[mt][i][3]);
   __syncthreads();
+  Q40_STAMP(5);
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");     // every CTA of the cluster is running
   {
     const float* sl = reinterpret_cast<const float*>(slab);
     const int total = p.M * F_SPAN_COLS;
@@ -273,49 +344,44 @@ gemv_tiled_kernel(const TiledParams p) {
       const int grp = lc >> 6, jt = (lc >> 4) & 3, r = lc & 15;
       const int mt = m >> 3, mm = m & 7;
       const int fl = (r & 7) * 4 + (mm >> 1);
-      const int off = (((mt * 4 + jt) * 32 + fl) << 2) + (mm & 1) + 2 * (r >> 3);
+      const int off = (((mt * NT + (grp % NG) * 4 + jt) * 32 + fl) << 2) + (mm & 1) + 2 * (r >> 3);
       float v = 0.f;
 #pragma unroll
-      for (int ks = 0; ks < KS; ++ks) v += sl[off + (grp + 4 * ks) * (MT * 4 * 32 * 4)];   // the k slices of the group
-      cta_part[idx] = v;
+      for (int ks = 0; ks < KS; ++ks)        // the k slices of the group
+        v += sl[off + (grp / NG + NGW * ks) * (MT * NT * 32 * 4)];
+      float* dst = cluster.map_shared_rank(recv, lc / slice);
+      dst[(rank * p.M + m) * slice + (lc % slice)] = v;
     }
   }
-  cluster.sync();
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  Q40_STAMP(6);
 
-  // ---- split-K over the cluster: rank r finishes columns [r*slice, (r+1)*slice) of the span ----
-  const int nranks = (int)cluster.num_blocks();
-  const int rank = (int)cluster.block_rank();
-  const int slice = F_SPAN_COLS / nranks;            // 16, 32, 64, 128 or 256
+  // ---- split-K over the cluster: rank r finishes columns [r*slice, (r+1)*slice) of the span from the
+  // partials it received (added in rank order) ----
   const int npart = (EPI == EPI_SILU) ? nranks / 2 : nranks;
   for (int m = warp; m < p.M; m += FW) {
     float ssq = 0.f;
     for (int cidx = lane; cidx < slice; cidx += 32) {
       const int lc = rank * slice + cidx;
-      const int idx = m * F_SPAN_COLS + lc;
-      // all remote loads are issued before the first add; the adds keep rank order
+      const float* rp = recv + m * slice + cidx;
+      const int rstride = p.M * slice;
       float v0 = 0.f, v1 = 0.f;
       if (EPI == EPI_SILU) {
-        float t0[8], t1[8];
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          t0[r] = (r < npart) ? *cluster.map_shared_rank(cta_part + idx, 2 * r) : 0.f;       // w1 partials
-          t1[r] = (r < npart) ? *cluster.map_shared_rank(cta_part + idx, 2 * r + 1) : 0.f;   // w3 partials
+        for (int r = 0; r < npart; ++r) {
+          v0 += rp[(2 * r) * rstride];         // w1 partials
+          v1 += rp[(2 * r + 1) * rstride];     // w3 partials
         }
-#pragma unroll
-        for (int r = 0; r < 8; ++r) { v0 += t0[r]; v1 += t1[r]; }
       } else {
-        float t0[16];
-#pragma unroll
-        for (int r = 0; r < 16; ++r) t0[r] = (r < npart) ? *cluster.map_shared_rank(cta_part + idx, r) : 0.f;
-#pragma unroll
-        for (int r = 0; r < 16; ++r) v0 += t0[r];
+        for (int r = 0; r < npart; ++r) v0 += rp[r * rstride];
       }
       const int n = f_span_col(span, lc);
       if (n < pr.N) {
         if (EPI == EPI_STORE) {
           pr.out[(int64_t)m * p.ldc + n] = __float2half_rn(v0);
         } else if (EPI == EPI_RESIDUAL) {
-          const __half hn = __hadd_rn(p.h_in[(int64_t)m * p.ldh + n], __float2half_rn(v0));
+          const __half hres = (m == warp && cidx == lane) ? h_first : p.h_in[(int64_t)m * p.ldh + n];
+          const __half hn = __hadd_rn(hres, __float2half_rn(v0));
           pr.out[(int64_t)m * p.ldc + n] = hn;
           const float f = __half2float(hn);
           ssq = fmaf(f, f, ssq);
@@ -331,22 +397,27 @@ gemv_tiled_kernel(const TiledParams p) {
       if (lane == 0) p.ss_out[(int64_t)m * p.ss_out_count + span * nranks + rank] = ssq;
     }
   }
-  cluster.sync();   // nobody leaves while a neighbour may still read its partial
+  Q40_STAMP(7);
+  Q40_TRACE_FLUSH(p.trace, 100 + 10 * PRO + EPI);
 }
 
-template <int MT, int PRO, int EPI>
+template <int MT, int NG, int KS, int PRO, int EPI>
 static int launch_tiled(const TiledParams& p, int grid_x, int nsplit, int cluster_x, cudaStream_t st, bool pdl) {
-  auto kern = gemv_tiled_kernel<MT, PRO, EPI>;
-  const size_t ring = (size_t)FW * F_DEPTH * F_SLOT_BYTES;
+  auto kern = gemv_tiled_kernel<MT, NG, KS, PRO, EPI>;
+  constexpr int FW = (4 / NG) * KS, FT = FW * 32, NT = NG * 4;
+  const size_t ring = (size_t)FW * F_DEPTH * NG * F_GROUP_BYTES;
   const size_t xs = (size_t)MT * 8 * (p.rows_per_split + F_XS_PAD) * 2 + 64 + (size_t)p.rows_per_split * 2;
-  const size_t red = (size_t)FW * MT * 4 * 32 * 16 + (size_t)p.M * F_SPAN_COLS * 4;
-  const size_t smem = (ring + xs) > red ? (ring + xs) : red;
+  const size_t red = (size_t)FW * MT * NT * 32 * 16;
+  size_t smem = (ring + xs) > red ? (ring + xs) : red;
+  smem = (smem + 15) / 16 * 16;
+  TiledParams pp = p;
+  pp.recv_off = (int)smem;
+  smem += (size_t)p.M * F_SPAN_COLS * 4;        // receive buffer of the cluster reduction
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  if (cluster_x * nsplit > 8) {
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-    if (e != cudaSuccess) return (int)e;
-  }
+  // set on every variant, not only those that need it (see the note at q40_gemv_tiled)
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  if (e != cudaSuccess) return (int)e;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid_x, nsplit, 1);
   cfg.blockDim = dim3(FT, 1, 1);
@@ -371,7 +442,7 @@ static int launch_tiled(const TiledParams& p, int grid_x, int nsplit, int cluste
     }
   }
   cfg.numAttrs = pdl ? 2 : 1;
-  e = cudaLaunchKernelEx(&cfg, kern, p);
+  e = cudaLaunchKernelEx(&cfg, kern, pp);
   if (e != cudaSuccess) return (int)e;
   return Q40_OK;
 }
@@ -386,9 +457,11 @@ extern "C" int q40_gemv_tiled(int mode, int nmat, const void* const* bw, const v
                               void* const* out, const int* n_cols, int64_t ldc, const void* a, int64_t lda,
                               int M, int K, const void* norm_w, const float* ss_in, int ss_in_count,
                               float eps, const void* h_in, int64_t ldh, float* ss_out, int ss_out_count,
-                              int max_cluster, int use_pdl, void* stream) {
+                              int max_cluster, int use_pdl, const void* const* prefetch,
+                              const size_t* prefetch_bytes, int n_prefetch, void* stream) {
   using namespace q40;
   using namespace q40::tiled;
+  if (n_prefetch < 0 || n_prefetch > 3 || (n_prefetch > 0 && (!prefetch || !prefetch_bytes))) return Q40_E_UNSUPPORTED;
   if (!bw || !out || !n_cols || !a) return Q40_E_NULL;
   if (mode < 0 || mode > 3 || nmat < 1 || nmat > 3) return Q40_E_UNSUPPORTED;
   if (mode == 3 && nmat != 2) return Q40_E_UNSUPPORTED;
@@ -418,6 +491,16 @@ extern "C" int q40_gemv_tiled(int mode, int nmat, const void* const* bw, const v
   p.a = (const __half*)a; p.lda = lda; p.ldc = ldc; p.M = M; p.K = K;
   p.norm_w = (const __half*)norm_w; p.ss_in = ss_in; p.ss_in_count = ss_in_count; p.eps = eps;
   p.h_in = (const __half*)h_in; p.ldh = ldh; p.ss_out = ss_out; p.ss_out_count = ss_out_count;
+#ifdef Q40_TRACE
+  p.trace = q40_trace_ptr;
+#endif
+  for (int i = 0; i < n_prefetch; ++i) {
+    if (!prefetch[i] || prefetch_bytes[i] == 0) continue;
+    if (!q40_aligned(prefetch[i], 16) || prefetch_bytes[i] % 16 != 0) return Q40_E_ALIGN;
+    if (prefetch_bytes[i] > 0xF0000000ull) return Q40_E_SHAPE;
+    p.pf[i] = (const uint8_t*)prefetch[i];
+    p.pf_bytes[i] = (uint32_t)prefetch_bytes[i];
+  }
 
   // split K over the cluster: as many splits as the cluster allows while a split keeps >= 64 rows,
   // and few enough CTAs to be resident at once (3 per SM)
@@ -432,22 +515,16 @@ extern "C" int q40_gemv_tiled(int mode, int nmat, const void* const* bw, const v
   cudaStream_t st = (cudaStream_t)stream;
   const bool pdl = use_pdl != 0;
   const int mt = (M <= 8) ? 1 : 2;
-#define Q40_TILED(MTV, PROV, EPIV) launch_tiled<MTV, PROV, EPIV>(p, grid_x, nsplit, cluster_x, st, pdl)
-  if (mt == 1) {
-    switch (mode) {
-      case 0: return Q40_TILED(1, PRO_NONE, EPI_STORE);
-      case 1: return Q40_TILED(1, PRO_NORM, EPI_STORE);
-      case 2: return Q40_TILED(1, PRO_NONE, EPI_RESIDUAL);
-      default: return Q40_TILED(1, PRO_NORM, EPI_SILU);
-    }
+#define Q40_TILED_MODES(MTV, NGV, KSV)                                                              \
+  switch (mode) {                                                                                    \
+    case 0: return launch_tiled<MTV, NGV, KSV, PRO_NONE, EPI_STORE>(p, grid_x, nsplit, cluster_x, st, pdl);    \
+    case 1: return launch_tiled<MTV, NGV, KSV, PRO_NORM, EPI_STORE>(p, grid_x, nsplit, cluster_x, st, pdl);    \
+    case 2: return launch_tiled<MTV, NGV, KSV, PRO_NONE, EPI_RESIDUAL>(p, grid_x, nsplit, cluster_x, st, pdl); \
+    default: return launch_tiled<MTV, NGV, KSV, PRO_NORM, EPI_SILU>(p, grid_x, nsplit, cluster_x, st, pdl);    \
   }
-  switch (mode) {
-    case 0: return Q40_TILED(2, PRO_NONE, EPI_STORE);
-    case 1: return Q40_TILED(2, PRO_NORM, EPI_STORE);
-    case 2: return Q40_TILED(2, PRO_NONE, EPI_RESIDUAL);
-    default: return Q40_TILED(2, PRO_NORM, EPI_SILU);
-  }
-#undef Q40_TILED
+  if (mt == 1) { Q40_TILED_MODES(1, 4, 4) }
+  Q40_TILED_MODES(2, 2, 2)
+#undef Q40_TILED_MODES
 }
 
 // Number of per-row sum-of-squares partials a mode-2 launch writes for this shape (so the caller can

@@ -217,6 +217,9 @@ class Transformer(nn.Module):
         self.use_tiled = True
         # width <= 16: rotary embedding, cache append and attention as one cluster launch
         self.use_fused_attn = False
+        self.fused_attn_max_width = 4   # widest step that uses the single-launch attention when it is on
+        # tiled path: each matmul launch hints the weights of the launches after it into L2
+        self.use_l2_prefetch = True
         self._layer_table = None
         self._trace = None       # optional int64 tensor [6 * n_layers + 8]: barrier timestamps of the step kernel
 
@@ -320,18 +323,28 @@ class Transformer(nn.Module):
             return self._decode_body_fused(B)
         return self._decode_body_unfused(B)
 
+    @staticmethod
+    def _tileable(lin):
+        return lin.kn()[1] % 256 == 0 and lin.kn()[0] % 16 == 0
+
+    def _tiled_of(self, lins):
+        """The rearranged copies of these layers' weights (made on first use)."""
+        out = []
+        for l in lins:
+            if getattr(l, "_tiled", None) is None or l._tiled_src != l.w.data_ptr():
+                l._tiled = K.relayout_tiled(l.w, l.s, l.kn())     # one-time rearranged copy
+                l._tiled_src = l.w.data_ptr()
+            out.append(l._tiled)
+        return out
+
     def _fused(self, mode, lins, outs, ldc, a, lda, M, norm_w=None, ss_in=None, ss_in_count=0, h_in=None,
-               ldh=0, ss_out=None, ss_out_count=0, st=None):
+               ldh=0, ss_out=None, ss_out_count=0, st=None, prefetch=()):
         import ctypes
         n = len(lins)
         P = ctypes.c_void_p * n
-        tiled = self.use_tiled and M <= 16 and all(l.kn()[1] % 256 == 0 and l.kn()[0] % 16 == 0 for l in lins)
+        tiled = self.use_tiled and M <= 16 and all(self._tileable(l) for l in lins)
         if tiled:
-            for l in lins:
-                if getattr(l, "_tiled", None) is None or l._tiled_src != l.w.data_ptr():
-                    l._tiled = K.relayout_tiled(l.w, l.s, l.kn())     # one-time rearranged copy
-                    l._tiled_src = l.w.data_ptr()
-            bw = P(*[l._tiled.data_ptr() for l in lins])
+            bw = P(*[t.data_ptr() for t in self._tiled_of(lins)])
         else:
             bw = P(*[l.w.data_ptr() for l in lins])
         bs = P(*[l.s.data_ptr() for l in lins])
@@ -344,7 +357,9 @@ class Transformer(nn.Module):
                                  ss_in.data_ptr() if ss_in is not None else None, ss_in_count,
                                  float(self.params.norm_eps), h_in.data_ptr() if h_in is not None else None, ldh,
                                  ss_out.data_ptr() if ss_out is not None else None, ss_out_count,
-                                 self.max_cluster, 1 if self.use_pdl else 0, st), "q40_gemv_fused")
+                                 self.max_cluster, 1 if self.use_pdl else 0,
+                                 *K._prefetch_args(self._tiled_of([l for l in prefetch if self._tileable(l)])
+                                                   if tiled else None), st), "q40_gemv_fused")
 
     def _decode_body_fused(self, B):
         """Decode step for B <= 16 branches: 7 launches per layer (qkv with RMSNorm prologue,
@@ -364,17 +379,23 @@ class Transformer(nn.Module):
         pos, plen, aws = self._pos_dev, self._prefix_len_dev, bufs["attn_ws"]
         check(lib.q40_embed_rows(self.tok_embeddings.weight.data_ptr(), self._tok_dev.data_ptr(), h.data_ptr(),
                                  ss_ffn.data_ptr(), c_ffn, B, p.dim, p.vocab_size, st), "q40_embed_rows")
-        for layer in self.layers:
+        pf = self.use_l2_prefetch and self.use_tiled
+        for li, layer in enumerate(self.layers):
             att, ff = layer.attention, layer.feed_forward
+            nxt = self.layers[li + 1].attention if li + 1 < len(self.layers) else None
+            # L2 hints: HBM is idle during the attention launches, so the qkv launch asks for wo, w1
+            # and w3; wo asks for w2; w1/w3 ask for the next layer's wq, wk, wv
             self._fused(1, [att.wq, att.wk, att.wv], [q, k, v], W, h, p.dim, B,
-                        norm_w=layer.attention_norm.weight, ss_in=ss_ffn, ss_in_count=c_ffn, st=st)
-            if self.use_fused_attn:
+                        norm_w=layer.attention_norm.weight, ss_in=ss_ffn, ss_in_count=c_ffn, st=st,
+                        prefetch=[att.wo, ff.w1, ff.w3] if pf else ())
+            if self.use_fused_attn and B <= self.fused_attn_max_width:
                 pk, pv = att.cache_prompt_k, att.cache_prompt_v
                 check(lib.q40_attn_tree_fused(qkv.data_ptr(), W, pk.data_ptr(), pv.data_ptr(), att.cache_k.data_ptr(),
                                               att.cache_k_s.data_ptr(), att.cache_v.data_ptr(),
                                               att.cache_v_s.data_ptr(), pos.data_ptr(), plen.data_ptr(),
                                               self._cos.data_ptr(), self._sin.data_ptr(), self._n_pos, ao.data_ptr(),
-                                              B, H, Hkv, D, p.max_seq_len, p.max_prompt_seq_len, st),
+                                              B, H, Hkv, D, p.max_seq_len, p.max_prompt_seq_len,
+                                              1 if self.use_pdl else 0, st),
                       "q40_attn_tree_fused")
             else:
                 check(lib.q40_rope_kv_append(q.data_ptr(), W, k.data_ptr(), W, v.data_ptr(), W, pos.data_ptr(),
@@ -390,9 +411,10 @@ class Transformer(nn.Module):
                                                v.data_ptr(), W, ao.data_ptr(), B, H, Hkv, D, aws.data_ptr(),
                                                aws.numel(), st), "q40_attn_tree_decode")
             self._fused(2, [att.wo], [h], p.dim, ao, H * D, B, h_in=h, ldh=p.dim, ss_out=ss_attn,
-                        ss_out_count=c_attn, st=st)
+                        ss_out_count=c_attn, st=st, prefetch=[ff.w2] if pf else ())
             self._fused(3, [ff.w1, ff.w3], [gbuf, gbuf], hid, h, p.dim, B, norm_w=layer.ffn_norm.weight,
-                        ss_in=ss_attn, ss_in_count=c_attn, st=st)
+                        ss_in=ss_attn, ss_in_count=c_attn, st=st,
+                        prefetch=[nxt.wq, nxt.wk, nxt.wv] if pf and nxt is not None else ())
             self._fused(2, [ff.w2], [h], p.dim, gbuf, hid, B, h_in=h, ldh=p.dim, ss_out=ss_ffn,
                         ss_out_count=c_ffn, st=st)
         self._norm(h, None, self.norm.weight, bufs["xn"], st)
@@ -526,11 +548,11 @@ class Transformer(nn.Module):
         buffers (`_tok_dev`, `_pos_dev`); returns the static logits buffer [B, vocab]."""
         fused = self.use_fused and B <= 16 and self.tp_world == 1
         mega = self.use_megakernel and B <= 8 and self.tp_world == 1
-        self.launches_per_step = 1 if mega else self.params.n_layers * ((5 if self.use_fused_attn else 7) if fused else 13) + (2 if fused else 1)
+        self.launches_per_step = 1 if mega else self.params.n_layers * ((5 if self.use_fused_attn and B <= self.fused_attn_max_width else 7) if fused else 13) + (2 if fused else 1)
         if not self.use_cuda_graph:
             return self._decode_body(B)
         key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster, self.use_megakernel,
-               self.use_tiled, self.use_fused_attn)
+               self.use_tiled, self.use_fused_attn, self.fused_attn_max_width, self.use_l2_prefetch)
         g = self._graphs.get(key)
         if g is None:
             # torch requires capture on a side stream after a warm-up run
@@ -545,7 +567,7 @@ class Transformer(nn.Module):
                     # this device cannot schedule 16-CTA clusters: use the portable size
                     self.max_cluster = 8
                     key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster,
-                           self.use_megakernel, self.use_tiled, self.use_fused_attn)
+                           self.use_megakernel, self.use_tiled, self.use_fused_attn, self.fused_attn_max_width, self.use_l2_prefetch)
                     self._decode_body(B)
             torch.cuda.current_stream(self.device).wait_stream(s)
             torch.cuda.synchronize(self.device)

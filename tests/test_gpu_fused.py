@@ -123,7 +123,11 @@ def test_layer_chain_modes_1_2_3(K, M, dims, tiled):
     g_np = g.cpu().numpy()
     h3, ss3 = K.gemv_fused(2, g, [D(w2, (hid, dim))], h_in=h2, use_pdl=True, tiled=tiled)
     ref3 = (h2_np.astype(np.float32) + O.matmul_q40(g_np, *w2, (hid, dim)).astype(np.float32)).astype(np.float16)
-    close(h3.cpu().numpy(), ref3)
+    # g is a product of two matmul outputs (|g| up to a few hundred here), so this output has a
+    # scale of hundreds; an fp16 rounding of one operand is 2^-11 of that scale, which the absolute
+    # floor has to admit for the few outputs that happen to land near zero
+    scale3 = float(np.abs(ref3.astype(np.float32)).mean())
+    close(h3.cpu().numpy(), ref3, atol=max(1e-2, 2e-3 * scale3))
     assert ss3.shape[1] == c_ffn
 
 

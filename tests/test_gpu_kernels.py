@@ -414,12 +414,15 @@ def test_rope_kv_append_and_tree_decode(K):
             hist_v[b].append(vd[b])
 
 
-def test_attn_tree_fused_matches_two_call_path(K):
+@pytest.mark.parametrize("plen,maxP,use_pdl", [(277, 300, 0), (277, 300, 1), (1100, 1200, 1), (0, 16, 1)])
+def test_attn_tree_fused_matches_two_call_path(K, plen, maxP, use_pdl):
     """The single-launch small-width attention (rotary + append + attention per cluster) against
-    q40_rope_kv_append + q40_attn_tree_decode: identical cache bytes, outputs within fp32 merge order."""
+    q40_rope_kv_append + q40_attn_tree_decode: identical cache bytes, outputs within fp32 merge
+    order.  1100 prompt keys exceed what the cluster holds in registers at once (768), so that
+    case also runs the second batch of keys; an empty prompt leaves some key groups idle."""
     from spec_mcts_b200._lib import check, lib
     rng = np.random.default_rng(12)
-    B, H, Hkv, D, maxB, maxT, maxP, plen, n_pos = 5, 8, 4, 128, 6, 40, 300, 277, 400
+    B, H, Hkv, D, maxB, maxT, n_pos = 5, 8, 4, 128, 6, 40, maxP + 100
     W = (H + 2 * Hkv) * D
     cos, sin = O.rope_tables(D, n_pos, 1e6)
     cos_d, sin_d = dev(np.ascontiguousarray(cos[:, :64])), dev(np.ascontiguousarray(sin[:, :64]))
@@ -448,7 +451,7 @@ def test_attn_tree_fused_matches_two_call_path(K):
         check(lib.q40_attn_tree_fused(qkv.data_ptr(), W, pk.data_ptr(), pv.data_ptr(), kq2.data_ptr(), ks2.data_ptr(),
                                       vq2.data_ptr(), vs2.data_ptr(), pos_d.data_ptr(), plen_d.data_ptr(),
                                       cos_d.data_ptr(), sin_d.data_ptr(), n_pos, o2.data_ptr(), B, H, Hkv, D, maxT,
-                                      maxP, st))
+                                      maxP, use_pdl, st))
         assert torch.equal(kq1, kq2) and torch.equal(vq1, vq2)
         assert torch.equal(ks1.view(torch.int16), ks2.view(torch.int16))
         assert torch.equal(vs1.view(torch.int16), vs2.view(torch.int16))
