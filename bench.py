@@ -42,6 +42,11 @@ N_LAYERS, DIM, HEADS, FFN, VOCAB = 32, 4096, 32, 11008, 32016
 LAYER_SHAPES = [(4096, 4096)] * 4 + [(11008, 4096), (11008, 4096), (4096, 11008)]   # (N, K): q k v o w1 w3 w2
 
 
+# ncu dram__bytes_read.sum + dram__bytes_write.sum of the four tiled matmul launches of one 7B layer
+# at width 1, averaged per launch (filled in from the capture under profiles/)
+TILED_TRAFFIC_PER_LAUNCH = 26.9e6
+
+
 def q4_bytes(n, k, m, group=64):
     """Algorithmic bytes of one fused dequant-matmul: packed weight + scales + A + C."""
     return n * k // 2 + n * k // group * 2 + 2 * m * k + 2 * m * n
@@ -167,8 +172,6 @@ def build_model(device):
     if "Q40_FATTN" in os.environ:
         model.fused_attn_max_width = int(os.environ["Q40_FATTN"])
         model.use_fused_attn = model.fused_attn_max_width > 0
-    if "Q40_L2PF" in os.environ:
-        model.use_l2_prefetch = os.environ["Q40_L2PF"] != "0"
     if "Q40_CLUSTER" in os.environ:
         model.max_cluster = int(os.environ["Q40_CLUSTER"])
     return model
@@ -263,13 +266,12 @@ def gemv_roofline(model, width, reps):
 
     def one_pass():
         st = torch.cuda.current_stream(dev).cuda_stream
-        for gi, grp in enumerate(groups):
+        for grp in groups:
             k, n = grp[0].kn()
             if fused:
                 W = n * len(grp)
                 outs = [out[:, i * n:(i + 1) * n] for i in range(len(grp))]
-                nxt = groups[gi + 1] if model.use_l2_prefetch and gi + 1 < len(groups) else ()
-                model._fused(0, grp, outs, 3 * FFN, xs[k], k, width, st=st, prefetch=nxt)
+                model._fused(0, grp, outs, 3 * FFN, xs[k], k, width, st=st)
             else:
                 check(lib.q40_gemm_kn(xs[k].data_ptr(), k, grp[0].w.data_ptr(), grp[0].s.data_ptr(), out.data_ptr(),
                                       3 * FFN, width, n, k, 64, ws.data_ptr(), ws.numel(), st))
@@ -296,7 +298,13 @@ def gemv_roofline(model, width, reps):
     passes = (width + 15) // 16 if not fused else 1
     launches = reps * len(groups) * passes
     total_bytes = reps * sum(q4_bytes(l.kn()[1], l.kn()[0], width) for grp in groups for l in grp)
-    name = "gemv_fused_kernel<%d,0,0>" % (1 if width <= 8 else 2) if fused else "gemv_kn_kernel<64,%d>" % (1 if width <= 8 else 2)
+    mt = 1 if width <= 8 else 2
+    if fused and model.use_tiled:
+        name = "gemv_tiled_kernel<%d,%s,0,0>" % (mt, "4,4" if mt == 1 else "2,2")
+    elif fused:
+        name = "gemv_fused_kernel<%d,0,0>" % mt
+    else:
+        name = "gemv_kn_kernel<64,%d>" % mt
     return total_bytes / sec / 1e9, sec / launches, total_bytes / launches, name
 
 
@@ -474,9 +482,9 @@ def main():
             "roofline": {"bound": "hbm", "kernel": roof_kernel, "achieved": ach, "peak": hbm_peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": ach / hbm_peak,
                          "avg_launch_us": sec_per_launch * 1e6, "alg_bytes_per_launch": bytes_per_launch,
-                         # dram read+write bytes per launch from the ncu capture summarised in
-                         # profiles/gemv_fused_kernel_7b_shapes_ncu_full.md (traffic == algorithmic bytes)
-                         "traffic": 26.9e6 if roof_kernel.startswith("gemv_fused") else None},
+                         # dram read+write bytes per average launch from the ncu capture summarised in
+                         # profiles/gemv_tiled_kernel_7b_shapes_ncu.md (traffic == algorithmic bytes)
+                         "traffic": TILED_TRAFFIC_PER_LAUNCH if roof_kernel.startswith("gemv_tiled") else None},
             "e2e": {"value": e2e_tok_s[w0], "unit": UNIT, "h2d_bytes_per_step": e2e_res[w0][1],
                     "d2h_bytes_per_step": e2e_res[w0][2]},
             "gpu_launches": steps * model.launches_per_step,

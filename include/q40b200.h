@@ -143,17 +143,11 @@ int q40_relayout_tiled(const void* bw, const void* bs, void* out, int N, int K, 
 
 /* q40_gemv_fused on tiled copies (same modes, arguments and results up to rounding: the scale is
  * applied to the activations, fp16(scale*x), instead of to the weight; 1 <= M <= 16; every
- * N % 256 == 0).  bw[i] are the tiled streams; bs is ignored and may be NULL.
- * prefetch[0..n_prefetch) (n_prefetch <= 3, host arrays read during the call; 16-byte aligned
- * device ranges of prefetch_bytes[i] % 16 == 0 bytes) are requested into L2 while this launch
- * runs: pass the weight streams of the launches that follow on the stream, so that HBM keeps
- * streaming while those launches wait for their inputs.  The ranges are only hinted, never
- * dereferenced by the SMs; n_prefetch = 0 turns the hint off. */
+ * N % 256 == 0).  bw[i] are the tiled streams; bs is ignored and may be NULL. */
 int q40_gemv_tiled(int mode, int nmat, const void* const* bw, const void* const* bs, void* const* out,
                    const int* n_cols, int64_t ldc, const void* a, int64_t lda, int M, int K,
                    const void* norm_w, const float* ss_in, int ss_in_count, float eps, const void* h_in,
                    int64_t ldh, float* ss_out, int ss_out_count, int max_cluster, int use_pdl,
-                   const void* const* prefetch, const size_t* prefetch_bytes, int n_prefetch,
                    void* stream);
 int q40_gemv_tiled_ss_count(int N, int K, int max_cluster);
 

@@ -55,7 +55,7 @@ SIGNATURES = {
     "q40_gemv_fused_ss_count": (c_int, [c_int, c_int, c_int]),
     "q40_gemv_tiled": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
                                c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int64, c_void_p,
-                               c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+                               c_int, c_int, c_int, c_void_p]),
     "q40_gemv_tiled_ss_count": (c_int, [c_int, c_int, c_int]),
     "q40_tiled_bytes": (c_size_t, [c_int, c_int]),
     "q40_relayout_tiled": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),

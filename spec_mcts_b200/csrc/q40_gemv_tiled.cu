@@ -41,7 +41,6 @@ constexpr int T_STEP_BYTES = 2048 + 128;    // one step in the tiled stream: wei
 constexpr int F_SPAN_BYTES = 128;
 constexpr int F_SPAN_COLS = 256;
 constexpr int F_XS_PAD = 16;
-constexpr int PF_CHUNK = 4096;              // bytes per L2 prefetch request
 
 enum { PRO_NONE = 0, PRO_NORM = 1 };
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2 };
@@ -69,9 +68,6 @@ struct TiledParams {
   int64_t ldh;
   float* ss_out;
   int ss_out_count;
-  // weight streams a later launch will read: requested into L2 while this launch runs
-  const uint8_t* pf[3];
-  uint32_t pf_bytes[3];
   void* trace;             // stage timestamps (trace builds only)
   int recv_off;            // byte offset of the receive buffer in dynamic shared memory
 };
@@ -172,21 +168,6 @@ gemv_tiled_kernel(const TiledParams p) {
   for (int j = 0; j < F_DEPTH; ++j) {
     if (j < my_steps) issue(j, j);
     f_commit();
-  }
-  // ---- ask L2 for the weight streams of the launches that follow (fire and forget): the dependent
-  // launches cannot start their own loads early enough to keep HBM busy across the hand-over ----
-  if (warp == FW - 1) {
-    const uint32_t ncta = gridDim.x * gridDim.y, cta = blockIdx.y * gridDim.x + blockIdx.x;
-#pragma unroll
-    for (int i = 0; i < 3; ++i) {
-      const uint32_t bytes = p.pf_bytes[i];
-      const uint32_t nchunks = (bytes + PF_CHUNK - 1) / PF_CHUNK;
-      for (uint32_t c = cta * 32 + lane; c < nchunks; c += ncta * 32) {
-        const uint32_t off = c * PF_CHUNK;
-        const uint32_t sz = min((uint32_t)PF_CHUNK, bytes - off);     // a multiple of 16 (checked by the host)
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.pf[i] + off), "r"(sz) : "memory");
-      }
-    }
   }
   Q40_STAMP(1);
   asm volatile("griddepcontrol.launch_dependents;");
@@ -457,11 +438,9 @@ extern "C" int q40_gemv_tiled(int mode, int nmat, const void* const* bw, const v
                               void* const* out, const int* n_cols, int64_t ldc, const void* a, int64_t lda,
                               int M, int K, const void* norm_w, const float* ss_in, int ss_in_count,
                               float eps, const void* h_in, int64_t ldh, float* ss_out, int ss_out_count,
-                              int max_cluster, int use_pdl, const void* const* prefetch,
-                              const size_t* prefetch_bytes, int n_prefetch, void* stream) {
+                              int max_cluster, int use_pdl, void* stream) {
   using namespace q40;
   using namespace q40::tiled;
-  if (n_prefetch < 0 || n_prefetch > 3 || (n_prefetch > 0 && (!prefetch || !prefetch_bytes))) return Q40_E_UNSUPPORTED;
   if (!bw || !out || !n_cols || !a) return Q40_E_NULL;
   if (mode < 0 || mode > 3 || nmat < 1 || nmat > 3) return Q40_E_UNSUPPORTED;
   if (mode == 3 && nmat != 2) return Q40_E_UNSUPPORTED;
@@ -494,13 +473,6 @@ extern "C" int q40_gemv_tiled(int mode, int nmat, const void* const* bw, const v
 #ifdef Q40_TRACE
   p.trace = q40_trace_ptr;
 #endif
-  for (int i = 0; i < n_prefetch; ++i) {
-    if (!prefetch[i] || prefetch_bytes[i] == 0) continue;
-    if (!q40_aligned(prefetch[i], 16) || prefetch_bytes[i] % 16 != 0) return Q40_E_ALIGN;
-    if (prefetch_bytes[i] > 0xF0000000ull) return Q40_E_SHAPE;
-    p.pf[i] = (const uint8_t*)prefetch[i];
-    p.pf_bytes[i] = (uint32_t)prefetch_bytes[i];
-  }
 
   // split K over the cluster: as many splits as the cluster allows while a split keeps >= 64 rows,
   // and few enough CTAs to be resident at once (3 per SM)

@@ -222,9 +222,8 @@ def relayout_tiled(b_w: torch.Tensor, b_s: torch.Tensor, b_shape) -> torch.Tenso
 
 
 def gemv_fused(mode: int, a: torch.Tensor, weights, *, norm_w=None, ss_in=None, eps: float = 1e-5, h_in=None,
-               max_cluster: int = 16, use_pdl: bool = False, tiled: bool = False, prefetch=()):
+               max_cluster: int = 16, use_pdl: bool = False, tiled: bool = False):
     """Decode-step matmul(s) with fused neighbours (q40_gemv_fused in include/q40b200.h).
-    `prefetch` (tiled only): up to three uint8 tensors hinted into L2 during the launch.
     `weights` is a list of 1-3 (b_w, b_s, (K, N)) triples sharing the activations a [M <= 16, K].
     mode 0: [a @ deq(B_i)]; 1: RMSNorm(a; norm_w, ss_in) first; 2: returns (h_in + a @ deq(B),
     ss_out [M, count]); 3: silu(RMSNorm(a) @ deq(B_0)) * (RMSNorm(a) @ deq(B_1))."""
@@ -260,26 +259,12 @@ def gemv_fused(mode: int, a: torch.Tensor, weights, *, norm_w=None, ss_in=None, 
                              P(*[o.data_ptr() for o in outs]), (ctypes.c_int * n)(*Ns), ldc, a.data_ptr(),
                              a.stride(0), M, K, _ptr(norm_w), _ptr(ss_in), ss_in.shape[1] if ss_in is not None else 0,
                              float(eps), _ptr(h_in), h_in.stride(0) if h_in is not None else 0, _ptr(ss_out), cnt,
-             max_cluster, 1 if use_pdl else 0, *_prefetch_args(prefetch if tiled else None), _stream(dev)),
-          "q40_gemv_fused")
+             max_cluster, 1 if use_pdl else 0, _stream(dev)), "q40_gemv_fused")
     if mode == 2:
         return outs[0], ss_out
     if mode == 3:
         return outs[0]
     return outs
-
-
-def _prefetch_args(tensors):
-    """(pointer array, byte-count array, count) of q40_gemv_tiled's L2 hint; () for the entry
-    points that have none."""
-    import ctypes
-    if tensors is None:
-        return ()
-    n = len(tensors)
-    if n == 0:
-        return (None, None, 0)
-    return ((ctypes.c_void_p * n)(*[t.data_ptr() for t in tensors]),
-            (ctypes.c_size_t * n)(*[t.numel() * t.element_size() for t in tensors]), n)
 
 
 def embed_rows(emb: torch.Tensor, tokens: torch.Tensor, ss_count: int):

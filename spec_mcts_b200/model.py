@@ -216,10 +216,10 @@ class Transformer(nn.Module):
         # B <= 16: the fused matmuls read a rearranged ("tiled") copy of each weight, made on first use
         self.use_tiled = True
         # width <= 16: rotary embedding, cache append and attention as one cluster launch
-        self.use_fused_attn = False
-        self.fused_attn_max_width = 4   # widest step that uses the single-launch attention when it is on
-        # tiled path: each matmul launch hints the weights of the launches after it into L2
-        self.use_l2_prefetch = True
+        # single-launch attention (rotary + append + attention) up to this width; wider steps read the
+        # shared prompt once for all branches with the three-launch path
+        self.use_fused_attn = True
+        self.fused_attn_max_width = 1
         self._layer_table = None
         self._trace = None       # optional int64 tensor [6 * n_layers + 8]: barrier timestamps of the step kernel
 
@@ -338,7 +338,7 @@ class Transformer(nn.Module):
         return out
 
     def _fused(self, mode, lins, outs, ldc, a, lda, M, norm_w=None, ss_in=None, ss_in_count=0, h_in=None,
-               ldh=0, ss_out=None, ss_out_count=0, st=None, prefetch=()):
+               ldh=0, ss_out=None, ss_out_count=0, st=None):
         import ctypes
         n = len(lins)
         P = ctypes.c_void_p * n
@@ -357,9 +357,7 @@ class Transformer(nn.Module):
                                  ss_in.data_ptr() if ss_in is not None else None, ss_in_count,
                                  float(self.params.norm_eps), h_in.data_ptr() if h_in is not None else None, ldh,
                                  ss_out.data_ptr() if ss_out is not None else None, ss_out_count,
-                                 self.max_cluster, 1 if self.use_pdl else 0,
-                                 *K._prefetch_args(self._tiled_of([l for l in prefetch if self._tileable(l)])
-                                                   if tiled else None), st), "q40_gemv_fused")
+                                 self.max_cluster, 1 if self.use_pdl else 0, st), "q40_gemv_fused")
 
     def _decode_body_fused(self, B):
         """Decode step for B <= 16 branches: 7 launches per layer (qkv with RMSNorm prologue,
@@ -379,15 +377,10 @@ class Transformer(nn.Module):
         pos, plen, aws = self._pos_dev, self._prefix_len_dev, bufs["attn_ws"]
         check(lib.q40_embed_rows(self.tok_embeddings.weight.data_ptr(), self._tok_dev.data_ptr(), h.data_ptr(),
                                  ss_ffn.data_ptr(), c_ffn, B, p.dim, p.vocab_size, st), "q40_embed_rows")
-        pf = self.use_l2_prefetch and self.use_tiled
-        for li, layer in enumerate(self.layers):
+        for layer in self.layers:
             att, ff = layer.attention, layer.feed_forward
-            nxt = self.layers[li + 1].attention if li + 1 < len(self.layers) else None
-            # L2 hints: HBM is idle during the attention launches, so the qkv launch asks for wo, w1
-            # and w3; wo asks for w2; w1/w3 ask for the next layer's wq, wk, wv
             self._fused(1, [att.wq, att.wk, att.wv], [q, k, v], W, h, p.dim, B,
-                        norm_w=layer.attention_norm.weight, ss_in=ss_ffn, ss_in_count=c_ffn, st=st,
-                        prefetch=[att.wo, ff.w1, ff.w3] if pf else ())
+                        norm_w=layer.attention_norm.weight, ss_in=ss_ffn, ss_in_count=c_ffn, st=st)
             if self.use_fused_attn and B <= self.fused_attn_max_width:
                 pk, pv = att.cache_prompt_k, att.cache_prompt_v
                 check(lib.q40_attn_tree_fused(qkv.data_ptr(), W, pk.data_ptr(), pv.data_ptr(), att.cache_k.data_ptr(),
@@ -411,10 +404,9 @@ class Transformer(nn.Module):
                                                v.data_ptr(), W, ao.data_ptr(), B, H, Hkv, D, aws.data_ptr(),
                                                aws.numel(), st), "q40_attn_tree_decode")
             self._fused(2, [att.wo], [h], p.dim, ao, H * D, B, h_in=h, ldh=p.dim, ss_out=ss_attn,
-                        ss_out_count=c_attn, st=st, prefetch=[ff.w2] if pf else ())
+                        ss_out_count=c_attn, st=st)
             self._fused(3, [ff.w1, ff.w3], [gbuf, gbuf], hid, h, p.dim, B, norm_w=layer.ffn_norm.weight,
-                        ss_in=ss_attn, ss_in_count=c_attn, st=st,
-                        prefetch=[nxt.wq, nxt.wk, nxt.wv] if pf and nxt is not None else ())
+                        ss_in=ss_attn, ss_in_count=c_attn, st=st)
             self._fused(2, [ff.w2], [h], p.dim, gbuf, hid, B, h_in=h, ldh=p.dim, ss_out=ss_ffn,
                         ss_out_count=c_ffn, st=st)
         self._norm(h, None, self.norm.weight, bufs["xn"], st)
@@ -552,7 +544,7 @@ class Transformer(nn.Module):
         if not self.use_cuda_graph:
             return self._decode_body(B)
         key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster, self.use_megakernel,
-               self.use_tiled, self.use_fused_attn, self.fused_attn_max_width, self.use_l2_prefetch)
+               self.use_tiled, self.use_fused_attn, self.fused_attn_max_width)
         g = self._graphs.get(key)
         if g is None:
             # torch requires capture on a side stream after a warm-up run
@@ -567,7 +559,7 @@ class Transformer(nn.Module):
                     # this device cannot schedule 16-CTA clusters: use the portable size
                     self.max_cluster = 8
                     key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster,
-                           self.use_megakernel, self.use_tiled, self.use_fused_attn, self.fused_attn_max_width, self.use_l2_prefetch)
+                           self.use_megakernel, self.use_tiled, self.use_fused_attn, self.fused_attn_max_width)
                     self._decode_body(B)
             torch.cuda.current_stream(self.device).wait_stream(s)
             torch.cuda.synchronize(self.device)
