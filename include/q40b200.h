@@ -78,7 +78,7 @@ int q40_gemm_kn(const void* a, int64_t lda, const void* bw, const void* bs, void
                 int64_t ldc, int M, int N, int K, int group, void* workspace,
                 size_t workspace_bytes, void* stream);
 
-/* The tensor-core form q40_gemm_kn selects for M > 16 (group 64, K % 64 == 0, N % 128 == 0):
+/* The tensor-core form q40_gemm_kn selects for M > 16 (group 64, K % 64 == 0, N % 128 == 0, even ldc, lda % 8 == 0):
  * tcgen05.mma with the 128 output features of a packed block as the MMA M dimension and the
  * batch as N, accumulator in tensor memory, split-K over a thread-block cluster.  `err` is a
  * device int (zeroed by the caller) that the kernel sets to 1 if one of its bounded waits

@@ -528,7 +528,7 @@ extern "C" int q40_gemm_kn(const void* a, int64_t lda, const void* bw, const voi
   __half* ch = (__half*)c;
   // batches above 16 rows go to the tcgen05 kernel when the shape allows it; its error word is the
   // last int of the (zeroed) counter header of the workspace
-  if (M > 16 && group == 64 && K % 64 == 0 && workspace && workspace_bytes >= (size_t)q40::COUNTER_BYTES &&
+  if (M > 16 && group == 64 && K % 64 == 0 && N % 128 == 0 && ldc % 2 == 0 && lda % 8 == 0 && workspace && workspace_bytes >= (size_t)q40::COUNTER_BYTES &&
       p.nspans * 4 <= q40::COUNTER_BYTES - 4)
     return q40_gemm_kn_tc(a, lda, bw, bs, c, ldc, M, N, K,
                           reinterpret_cast<int*>((char*)workspace + q40::COUNTER_BYTES - 4), stream);

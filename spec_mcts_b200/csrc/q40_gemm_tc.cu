@@ -5,15 +5,21 @@
 // one packed 64-byte block of the weight matrix are the MMA's M dimension and the batch rows
 // its N dimension (padded to a multiple of 16, up to 256), so hardly any tensor work is spent on
 // padding.  Per 64-row k block a CTA
-//   * loads 64 x 64 packed bytes and their scale pairs into registers (prefetched one block
-//     ahead), turns the nibbles into fp16(code * scale) — the reference's operand value,
+//   * has its 64 x 64 packed bytes and scale pairs copied asynchronously into a lane-private ring
+//     (the HBM stream), turns the nibbles into fp16(code * scale) — the reference's operand value,
 //     triton_kernels.py:444-445 — and stores them as the A operand in MN-major, 128-byte-swizzled
 //     shared memory: the 64 high-nibble features are one 128-byte row segment per k, the 64
 //     low-nibble features the other (inside each group of four the features sit in the order
 //     0,2,1,3, which is undone when the accumulator is read back);
-//   * copies the 64-wide slice of the activations as the K-major B operand;
-//   * one thread issues four tcgen05.mma (K = 16 each) that accumulate into tensor memory, and
-//     a tcgen05.commit on the stage's mbarrier lets the stage be refilled three blocks later.
+//   * has the 64-wide slice of the activations copied asynchronously straight into the K-major,
+//     swizzled B operand;
+//   * one more warp issues four tcgen05.mma (K = 16 each) that accumulate into tensor memory as soon
+//     as the block's producers have arrived on its "full" mbarrier, and a tcgen05.commit on the
+//     stage's "free" mbarrier lets the stage be refilled.
+// The eight producer warps work as G groups (4, or 2 above 112 batch rows where shared memory is the
+// limit) that take the k blocks in turn, each with its own A stage: a group's chain of waits, copies,
+// dequantisation, proxy fence and arrival spans G blocks of tensor-core time, and its copies for its
+// next block (G blocks ahead) are in flight meanwhile.  There is no CTA-wide barrier in the loop.
 // The k range is split over a thread-block cluster; the partial accumulators are exchanged
 // through distributed shared memory (no global scratch).  Every mbarrier wait is bounded: on
 // expiry the kernel records an error code, skips the remaining work, frees its tensor memory
@@ -21,6 +27,7 @@
 //
 // Replaces matmul_q40_kernel (triton_kernels.py:357-469) for M > 16.
 #include <cooperative_groups.h>
+#include <cstdio>
 
 #include "q40_common.cuh"
 
@@ -28,11 +35,12 @@ namespace cg = cooperative_groups;
 
 namespace q40 {
 
-constexpr int TC_THREADS = 256;
+constexpr int TC_THREADS = 256;                // producer threads (8 warps; 16 measured no faster)
+constexpr int TC_BLOCK = TC_THREADS + 32;      // + the warp that issues the MMAs
 constexpr int TC_BK = 64;                      // k rows per pipeline stage
-constexpr int TC_STAGES = 3;
 constexpr int TC_TILE_N = 128;                 // output features per CTA
-constexpr int TC_A_BYTES = TC_TILE_N * TC_BK * 2;   // 16 KB
+constexpr int TC_A_BYTES = TC_TILE_N * TC_BK * 2;   // 16 KB per A stage
+constexpr int TC_MAX_G = 4;                    // most producer groups (= A stages) of any variant
 constexpr unsigned TC_SPIN_LIMIT = 1u << 22;   // polls of ~50 ns each before giving up
 
 struct TcParams {
@@ -44,6 +52,7 @@ struct TcParams {
   int64_t ldc;
   int M, N, K, Mpad, rows_per_split;
   int* err;             // device word, set non-zero when a bounded wait expired
+  void* trace;          // stage timestamps (trace builds only)
 };
 
 __device__ __forceinline__ uint32_t tc_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -97,130 +106,186 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 // features in the order 0,2,1,3
 __device__ __forceinline__ int tc_unpermute(int p) { return (p & ~3) | ((p & 1) << 1) | ((p >> 1) & 1); }
 
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__device__ __forceinline__ void tc_mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// NCOLS: tensor-memory columns of the accumulator, 32, 64, 128 or 256 (>= padded batch rows); G: producer
+// groups = A stages.  One CTA per SM: the runtime never co-schedules two CTAs of a kernel that allocates
+// tensor memory, so all latency hiding happens inside the CTA.
+template <int NCOLS, int G>
+__global__ void __launch_bounds__(TC_BLOCK, 1)
 gemm_tc_kernel(const TcParams p) {
   extern __shared__ unsigned char tc_smem_raw[];
   cg::cluster_group cluster = cg::this_cluster();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x, split = blockIdx.y;
+  Q40_TRACE_DECL
+  Q40_STAMP(0);
   const int kb = split * p.rows_per_split;
   const int ke = min(p.K, kb + p.rows_per_split);
   const int nblk = (ke - kb) / TC_BK;                       // host guarantees >= 1 and exact
-  const int b_bytes = p.Mpad * 128;                          // B stage: Mpad rows x 64 k x 2 B
-  const int stage_bytes = TC_A_BYTES + b_bytes;
+  const int b_bytes = p.Mpad * 128;                          // B slot: Mpad rows x 64 k x 2 B
+  constexpr int GT = TC_THREADS / G;                         // threads of a producer group
+  constexpr int TPR = GT / 64;                               // threads per k row (64 packed bytes)
+  constexpr int NQ = 4 / TPR;                                // 16-byte pieces per thread and block
+  constexpr int BSLOTS = 2 * G;                              // block b+G is copied into the slot block b-G used
+  constexpr int RAW_SLOT = 4096 + GT * 4;                    // a block's packed bytes + a scale pair per thread
 
-  // 1024-byte aligned carve-up: [stages][barriers][tmem slot]; the fp32 tile reuses the stages
+  // 1024-byte aligned carve-up: [A stages][B slots][raw rings: 2 slots per group][barriers][tmem slot];
+  // the fp32 tile of the epilogue reuses everything before the barriers
   const uint32_t raw = tc_smem_u32(tc_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* gbase = tc_smem_raw + (base - raw);
-  const uint32_t bars = base + TC_STAGES * stage_bytes;      // free[0..STAGES), done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + TC_STAGES * stage_bytes + 64);
+  const uint32_t b_base = base + G * TC_A_BYTES;
+  unsigned char* ring = gbase + G * TC_A_BYTES + BSLOTS * b_bytes;
+  const uint32_t ring_u32 = b_base + BSLOTS * b_bytes;
+  const uint32_t bars = ring_u32 + G * 2 * RAW_SLOT;         // free[0..G), done, full[0..G)
+  const uint32_t bar_done = bars + 8 * G, bar_full = bars + 8 * (G + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ring + G * 2 * RAW_SLOT + 8 * (2 * TC_MAX_G + 1));
+  volatile int* s_failed = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  if (tid == 0) *s_failed = 0;
 
-  int ncols = 32;
-  while (ncols < p.Mpad) ncols <<= 1;
+  constexpr int ncols = NCOLS;
 
   if (tid == 0) {
-    for (int s = 0; s <= TC_STAGES; ++s) tc_mbar_init(bars + 8 * s, 1);
+    for (int s = 0; s <= G; ++s) tc_mbar_init(bars + 8 * s, 1);
+    for (int s = 0; s < G; ++s) tc_mbar_init(bar_full + 8 * s, GT);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)), "r"(ncols));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)), "n"(ncols));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
+  Q40_STAMP(1);
 
   // instruction descriptor: D fp32, A/B fp16, A MN-major, B K-major, N = Mpad, M = 128
   const uint32_t idesc = (1u << 4) | (1u << 15) | ((uint32_t)(p.Mpad >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 
-  // this thread's share of a stage: 16 packed bytes of k row (tid / 4)
-  const int kr = tid >> 2, qd = tid & 3;
-  const int64_t w_ld = p.N / 2, s_ld = p.N / 64;
-  const uint8_t* wp = p.bw + (int64_t)(kb + kr) * w_ld + tile * 64 + 16 * qd;
-  const __half* sp = p.bs + (int64_t)(kb + kr) * s_ld + tile * 2;
-  uint4 wreg = __ldg(reinterpret_cast<const uint4*>(wp));
-  uint32_t sreg = __ldg(reinterpret_cast<const uint32_t*>(sp));
-
   bool failed = false;
-  for (int i = 0; i < nblk; ++i) {
-    const int s = i % TC_STAGES;
-    uint4 wnext = wreg;
-    uint32_t snext = sreg;
-    if (i + 1 < nblk) {
-      wnext = __ldg(reinterpret_cast<const uint4*>(wp + (int64_t)(i + 1) * TC_BK * w_ld));
-      snext = __ldg(reinterpret_cast<const uint32_t*>(sp + (int64_t)(i + 1) * TC_BK * s_ld));
-    }
-    if (i >= TC_STAGES) failed |= !tc_mbar_wait(bars + 8 * s, (uint32_t)((i / TC_STAGES - 1) & 1));
-
-    unsigned char* a_st = gbase + s * stage_bytes;
-    unsigned char* b_st = a_st + TC_A_BYTES;
-    // ---- A operand: row kr of k group kr/8; high nibbles -> feature chunk 0, low -> chunk 1 ----
-    {
+  if (warp < TC_THREADS / 32) {
+    // ================= producers: weights -> A operand, activations -> B operand =================
+    // group `grp` takes the k blocks grp, grp + G, ...; inside it, thread gt owns NQ 16-byte pieces of
+    // k row gt / TPR of every block
+    const int grp = tid / GT, gt = tid % GT;
+    const int kr = gt / TPR, q0 = (gt % TPR) * NQ;
+    const int64_t w_ld = p.N / 2, s_ld = p.N / 64;
+    const uint8_t* wp = p.bw + (int64_t)(kb + kr) * w_ld + tile * 64 + 16 * q0;
+    const __half* sp = p.bs + (int64_t)(kb + kr) * s_ld + tile * 2;
+    const uint32_t my_ring = ring_u32 + grp * 2 * RAW_SLOT;
+    unsigned char* my_ring_g = ring + grp * 2 * RAW_SLOT;
+    // raw weights of block blk into ring slot `rs`: piece q of row kr at [q][kr] (conflict-free reads)
+    auto issue_raw = [&](int blk, int rs) {
+      const uint32_t dst = my_ring + rs * RAW_SLOT;
+#pragma unroll
+      for (int q = 0; q < NQ; ++q)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + ((q0 + q) * 64 + kr) * 16),
+                     "l"(wp + (int64_t)blk * TC_BK * w_ld + 16 * q));
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4096 + gt * 4),
+                   "l"(sp + (int64_t)blk * TC_BK * s_ld));
+    };
+    // activations of block blk straight into B slot blk % BSLOTS: this thread copies chunk gt % 8
+    // (16 bytes) of the 128-byte k slice of rows gt / 8, + GT / 8, ...; rows beyond M are zero-filled
+    // (copy of size 0)
+    const int bm0 = gt >> 3, bjj = gt & 7;
+    const __half* bsrc = p.a + (int64_t)bm0 * p.lda + kb + 8 * bjj;
+    const uint32_t bdst = b_base + (bm0 >> 3) * 1024 + (bm0 & 7) * 128 + ((bjj ^ (bm0 & 7)) << 4);
+    auto issue_b = [&](int blk) {
+      const uint32_t dst = bdst + (blk % BSLOTS) * b_bytes;
+      const __half* src = bsrc + blk * TC_BK;
+      for (int m = bm0, j = 0; m < p.Mpad; m += GT / 8, ++j) {
+        const bool ok = m < p.M;
+        const int sz = ok ? 16 : 0;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + j * (GT / 64) * 1024),
+                     "l"(ok ? src + (int64_t)(GT / 8) * j * p.lda : p.a), "r"(sz));
+      }
+    };
+    if (grp < nblk) { issue_raw(grp, 0); issue_b(grp); }
+    asm volatile("cp.async.commit_group;");
+    unsigned char* a_st = gbase + grp * TC_A_BYTES;
+    for (int k = 0, blk = grp; blk < nblk; ++k, blk += G) {
+      // the MMAs of this group's previous block are done: its A stage and the B slot of block blk + G
+      // (the one block blk - G used) may be overwritten
+      if (k >= 1 && !tc_mbar_wait(bars + 8 * grp, (uint32_t)((k - 1) & 1))) { failed = true; break; }
+      if (blk + G < nblk) { issue_raw(blk + G, (k + 1) & 1); issue_b(blk + G); }
+      asm volatile("cp.async.commit_group;");
+      asm volatile("cp.async.wait_group 1;" ::: "memory");     // this thread's copies for block blk have landed
+      // ---- A operand: row kr of k group kr/8; high nibbles -> feature chunk 0, low -> chunk 1 ----
+      const unsigned char* slot = my_ring_g + (k & 1) * RAW_SLOT;
+      const uint32_t sreg = *reinterpret_cast<const uint32_t*>(slot + 4096 + gt * 4);
       const __half2 s_hi = __half2half2(__ushort_as_half((unsigned short)(sreg & 0xFFFF)));
       const __half2 s_lo = __half2half2(__ushort_as_half((unsigned short)(sreg >> 16)));
-      const uint32_t wds[4] = {wreg.x, wreg.y, wreg.z, wreg.w};
-      uint32_t hi[8], lo[8];
-#pragma unroll
-      for (int wi = 0; wi < 4; ++wi) {
-        const uint32_t w0 = wds[wi], w1 = w0 >> 8;
-        hi[2 * wi] = h2_as_u32(__hmul2(codes_hi_to_h2(w0), s_hi));       // features (0, 2) of the group of 4
-        hi[2 * wi + 1] = h2_as_u32(__hmul2(codes_hi_to_h2(w1), s_hi));   // features (1, 3)
-        lo[2 * wi] = h2_as_u32(__hmul2(codes_lo_to_h2(w0), s_lo));
-        lo[2 * wi + 1] = h2_as_u32(__hmul2(codes_lo_to_h2(w1), s_lo));
-      }
       const int kg = kr >> 3, r8 = kr & 7;
       unsigned char* row_hi = a_st + (kg * 2 + 0) * 1024 + r8 * 128;
       unsigned char* row_lo = a_st + (kg * 2 + 1) * 1024 + r8 * 128;
-      const int j0 = 2 * qd;            // 16 features = two 16-byte chunks of the 128-byte row
-      *reinterpret_cast<uint4*>(row_hi + (((j0) ^ r8) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-      *reinterpret_cast<uint4*>(row_hi + (((j0 + 1) ^ r8) << 4)) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
-      *reinterpret_cast<uint4*>(row_lo + (((j0) ^ r8) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-      *reinterpret_cast<uint4*>(row_lo + (((j0 + 1) ^ r8) << 4)) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
-    }
-    // ---- B operand: activations [Mpad, 64], K-major, rows beyond M are zero ----
-    {
-      const int k0 = kb + i * TC_BK;
-      for (int idx = tid; idx < p.Mpad * 8; idx += TC_THREADS) {
-        const int m = idx >> 3, j = idx & 7;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (m < p.M) v = *reinterpret_cast<const uint4*>(p.a + (int64_t)m * p.lda + k0 + 8 * j);
-        *reinterpret_cast<uint4*>(b_st + (m >> 3) * 1024 + (m & 7) * 128 + ((j ^ (m & 7)) << 4)) = v;
-      }
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy stores -> tensor core reads
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    failed = __syncthreads_or(failed ? 1 : 0) != 0;
-    if (failed) break;
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t a_u32 = base + s * stage_bytes, b_u32 = a_u32 + TC_A_BYTES;
 #pragma unroll
-      for (int ks = 0; ks < TC_BK / 16; ++ks) {
-        const uint64_t ad = tc_desc(a_u32 + ks * 4096, 1024, 2048);   // two k groups per MMA
-        const uint64_t bd = tc_desc(b_u32 + ks * 32, 16, 1024);       // 16 k = 32 bytes along the row
-        tc_mma(tmem, ad, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);
+      for (int q = 0; q < NQ; ++q) {
+        const uint4 wreg = *reinterpret_cast<const uint4*>(slot + ((q0 + q) * 64 + kr) * 16);
+        const uint32_t wds[4] = {wreg.x, wreg.y, wreg.z, wreg.w};
+        uint32_t hi[8], lo[8];
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+          const uint32_t w0 = wds[wi], w1 = w0 >> 8;
+          hi[2 * wi] = h2_as_u32(__hmul2(codes_hi_to_h2(w0), s_hi));       // features (0, 2) of the group of 4
+          hi[2 * wi + 1] = h2_as_u32(__hmul2(codes_hi_to_h2(w1), s_hi));   // features (1, 3)
+          lo[2 * wi] = h2_as_u32(__hmul2(codes_lo_to_h2(w0), s_lo));
+          lo[2 * wi + 1] = h2_as_u32(__hmul2(codes_lo_to_h2(w1), s_lo));
+        }
+        const int j0 = 2 * (q0 + q);      // 16 features = two 16-byte chunks of the 128-byte row
+        *reinterpret_cast<uint4*>(row_hi + (((j0) ^ r8) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(row_hi + (((j0 + 1) ^ r8) << 4)) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+        *reinterpret_cast<uint4*>(row_lo + (((j0) ^ r8) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        *reinterpret_cast<uint4*>(row_lo + (((j0 + 1) ^ r8) << 4)) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
       }
-      tc_commit(bars + 8 * s);                      // stage s may be refilled when these MMAs are done
-      if (i == nblk - 1) tc_commit(bars + 8 * TC_STAGES);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> tensor core reads
+      tc_mbar_arrive(bar_full + 8 * grp);
+      if (blk == 0) Q40_STAMP(2);
     }
-    wreg = wnext;
-    sreg = snext;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  } else {
+    // ================= the MMA warp: lane 0 issues, the warp stays converged =================
+    // descriptors of A stage 0 / B slot 0; the others differ only in the 16-byte-granular start address
+    // field (the low 14 bits; all of shared memory is below 256 KB, so the additions cannot carry out)
+    const uint64_t ad_base = tc_desc(base, 1024, 2048);          // A: two k groups per MMA
+    const uint64_t bd_base = tc_desc(b_base, 16, 1024);          // B: 16 k = 32 bytes along the row
+    for (int i = 0; i < nblk; ++i) {
+      const int s = i % G;
+      if (!tc_mbar_wait(bar_full + 8 * s, (uint32_t)((i / G) & 1))) { failed = true; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (lane == 0) {
+        const uint64_t ad0 = ad_base + (uint64_t)((s * TC_A_BYTES) >> 4);
+        const uint64_t bd0 = bd_base + (uint64_t)(((i % BSLOTS) * b_bytes) >> 4);
+#pragma unroll
+        for (int ks = 0; ks < TC_BK / 16; ++ks)
+          tc_mma(tmem, ad0 + (uint64_t)((ks * 4096) >> 4), bd0 + (uint64_t)((ks * 32) >> 4), idesc,
+                 (i > 0 || ks > 0) ? 1u : 0u);
+        tc_commit(bars + 8 * s);                    // stage s may be refilled when these MMAs are done
+        if (i == nblk - 1) tc_commit(bar_done);
+      }
+      __syncwarp();
+    }
   }
-  if (!failed) failed = !tc_mbar_wait(bars + 8 * TC_STAGES, 0);
+  Q40_STAMP(3);
+  if (failed) *s_failed = 1;
+  if (!failed && !tc_mbar_wait(bar_done, 0)) *s_failed = 1;
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  failed = __syncthreads_or(failed ? 1 : 0) != 0;
+  __syncthreads();
+  failed = *s_failed != 0;
   if (failed && tid == 0) atomicExch(p.err, 1);
+  Q40_STAMP(4);
 
   // ---- accumulator -> fp32 tile in shared memory, [Mpad][128] with features in natural order ----
   float* tile_f = reinterpret_cast<float*>(gbase);
-  if (!failed) {
+  if (!failed && warp < TC_THREADS / 32) {
     const int q = warp & 3;                         // TMEM lanes 32q .. 32q+31 belong to this warp
     const int row = 32 * q + lane;                  // MMA row = feature slot
     const int feat = (row < 64) ? tc_unpermute(row) : 64 + tc_unpermute(row - 64);
     const int nchunk = p.Mpad / 16;
-    for (int ch = (warp >> 2); ch < nchunk; ch += 2) {   // warps 0-3 even chunks, warps 4-7 odd chunks
+    for (int ch = (warp >> 2); ch < nchunk; ch += TC_THREADS / 128) {   // four warps per chunk of 16 batch rows
       uint32_t r[16];
       tc_ld16(tmem + ((uint32_t)(32 * q) << 16) + ch * 16, r);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -232,32 +297,80 @@ gemm_tc_kernel(const TcParams p) {
   __syncthreads();
   if (warp == 0) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(ncols));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(ncols));
   }
+  Q40_STAMP(5);
   cluster.sync();
+  Q40_STAMP(6);
 
   // ---- split-K over the cluster: every rank finishes a slice of the (m, feature) pairs ----
   const int nranks = (int)cluster.num_blocks();
   const int rank = (int)cluster.block_rank();
-  const int total = p.M * TC_TILE_N;
-  const int per = (total + nranks - 1) / nranks;
+  const int total = p.M * TC_TILE_N;                       // a multiple of 128
+  const int per = ((total / 4 + nranks - 1) / nranks) * 4;
   const int e0 = rank * per, e1 = min(total, e0 + per);
   if (!failed) {
-    for (int e = e0 + tid; e < e1; e += TC_THREADS) {
-      float t[8];
+    for (int e = e0 + tid * 4; e < e1; e += TC_BLOCK * 4) {
+      float4 t[8];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) t[r] = (r < nranks) ? *cluster.map_shared_rank(tile_f + e, r) : 0.f;
-      float v = 0.f;
+      for (int r = 0; r < 8; ++r)
+        t[r] = (r < nranks) ? *reinterpret_cast<const float4*>(cluster.map_shared_rank(tile_f + e, r))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int r = 0; r < 8; ++r) v += t[r];
-      const int m = e / TC_TILE_N, n = tile * TC_TILE_N + e % TC_TILE_N;
-      if (n < p.N) p.c[(int64_t)m * p.ldc + n] = __float2half_rn(v);
+      for (int r = 0; r < 8; ++r) { v.x += t[r].x; v.y += t[r].y; v.z += t[r].z; v.w += t[r].w; }
+      const int m = e / TC_TILE_N, n = tile * TC_TILE_N + e % TC_TILE_N;      // four features of one row
+      if (n + 3 < p.N) {
+        __half2* dst = reinterpret_cast<__half2*>(p.c + (int64_t)m * p.ldc + n);
+        dst[0] = __floats2half2_rn(v.x, v.y);
+        dst[1] = __floats2half2_rn(v.z, v.w);
+      }
     }
   }
+  Q40_STAMP(7);
   cluster.sync();
+  Q40_TRACE_FLUSH(p.trace, 300);
 }
 
 }  // namespace q40
+
+// How many clusters of (1, nsplit) CTAs with this much dynamic shared memory run at once (cached per
+// shape of the question; 0 when the runtime cannot tell).
+using TcKernel = void (*)(const q40::TcParams);
+static int tc_groups_for(int mpad) { return mpad <= 112 ? 4 : 2; }      // what fits in shared memory
+static TcKernel tc_kernel_for(int mpad) {
+  if (mpad <= 32) return q40::gemm_tc_kernel<32, 4>;
+  if (mpad <= 64) return q40::gemm_tc_kernel<64, 4>;
+  if (mpad <= 112) return q40::gemm_tc_kernel<128, 4>;
+  if (mpad <= 128) return q40::gemm_tc_kernel<128, 2>;
+  return q40::gemm_tc_kernel<256, 2>;
+}
+static int tc_max_clusters(TcKernel kern, int mpad, int nsplit, size_t smem) {
+  static int cache[9][17] = {};          // [nsplit][padded rows / 16] -> fit + 1 (the shared memory size follows from the rows)
+  const int cls = mpad / 16;
+  if (cache[nsplit][cls]) return cache[nsplit][cls] - 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(1024, nsplit, 1);     // more clusters than any device holds: the answer is not capped
+  cfg.blockDim = dim3(q40::TC_BLOCK, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = nsplit;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    n = 0;
+  }
+#ifdef Q40_TRACE
+  fprintf(stderr, "tc_max_clusters(nsplit %d, smem %zu) = %d\n", nsplit, smem, n);
+#endif
+  cache[nsplit][cls] = n + 1;
+  return n;
+}
 
 // C[M,N] = A[M,K] @ deq(B)[K,N] for 16 < M, group 64, K % 64 == 0, N % 128 == 0, on tcgen05.
 // `err` is a device int the kernel sets to 1 if one of its bounded waits expires (results are then
@@ -267,15 +380,11 @@ extern "C" int q40_gemm_kn_tc(const void* a, int64_t lda, const void* bw, const 
   using namespace q40;
   if (!a || !bw || !bs || !c || !err) return Q40_E_NULL;
   if (M < 1 || N <= 0 || K <= 0 || N % 128 != 0 || K % TC_BK != 0) return Q40_E_SHAPE;
-  if (lda < K || ldc < N || lda % 8 != 0) return Q40_E_SHAPE;
+  if (lda < K || ldc < N || lda % 8 != 0 || ldc % 2 != 0) return Q40_E_SHAPE;
   if (!q40_aligned(a, 16) || !q40_aligned(bw, 16) || !q40_aligned(bs, 4)) return Q40_E_ALIGN;
   cudaStream_t st = (cudaStream_t)stream;
   const int tiles = N / TC_TILE_N;
   const int kblocks = K / TC_BK;
-  // split K over a cluster (<= 8) so that about one CTA per SM is busy, each with >= 4 k blocks
-  int nsplit = 1;
-  while (nsplit < 8 && tiles * nsplit * 2 <= 160 && kblocks % (nsplit * 2) == 0 && kblocks / (nsplit * 2) >= 4)
-    nsplit *= 2;
   const __half* ah = (const __half*)a;
   __half* ch = (__half*)c;
   for (int m0 = 0; m0 < M; m0 += 256) {
@@ -285,18 +394,35 @@ extern "C" int q40_gemm_kn_tc(const void* a, int64_t lda, const void* bw, const 
     p.bw = (const uint8_t*)bw; p.bs = (const __half*)bs;
     p.c = ch + (int64_t)m0 * ldc; p.ldc = ldc;
     p.M = mc; p.N = N; p.K = K; p.Mpad = (mc + 15) / 16 * 16;
-    p.rows_per_split = K / nsplit;
     p.err = err;
-    const size_t stage = (size_t)TC_A_BYTES + (size_t)p.Mpad * 128;
-    size_t smem = TC_STAGES * stage;
-    const size_t tile_f = (size_t)p.Mpad * TC_TILE_N * 4;
+#ifdef Q40_TRACE
+    p.trace = q40_trace_ptr;
+#endif
+    const int groups = tc_groups_for(p.Mpad);
+    size_t smem = (size_t)groups * TC_A_BYTES + (size_t)(2 * groups) * p.Mpad * 128;
+    const size_t tile_f = (size_t)p.Mpad * TC_TILE_N * 4;          // fp32 tile of the epilogue, same region
+    smem += (size_t)groups * 2 * (4096 + TC_THREADS / groups * 4);
     if (tile_f > smem) smem = tile_f;
     smem += 1024 /* alignment slack */ + 128 /* barriers + tmem slot */;
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    TcKernel kern = tc_kernel_for(p.Mpad);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
+    // split K over a cluster (<= 8): as many CTAs as the device holds at once (one per SM; the runtime
+    // is asked, because clusters cannot straddle GPCs), each with at least 4 k blocks; the last split
+    // may be shorter
+    int nsplit = 8, bps = 0;
+    for (; nsplit >= 1; nsplit >>= 1) {
+      bps = (kblocks + nsplit - 1) / nsplit;
+      if (nsplit > 1 && (bps < 4 || (nsplit - 1) * bps >= kblocks)) continue;
+      if (nsplit == 1) break;
+      const int fit = tc_max_clusters(kern, p.Mpad, nsplit, smem);
+      if (fit >= tiles) break;
+    }
+    if (nsplit < 1) { nsplit = 1; bps = kblocks; }
+    p.rows_per_split = bps * TC_BK;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(tiles, nsplit, 1);
-    cfg.blockDim = dim3(TC_THREADS, 1, 1);
+    cfg.blockDim = dim3(TC_BLOCK, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -306,7 +432,7 @@ extern "C" int q40_gemm_kn_tc(const void* a, int64_t lda, const void* bw, const 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel, p);
+    e = cudaLaunchKernelEx(&cfg, kern, p);
     if (e != cudaSuccess) return (int)e;
   }
   return Q40_OK;
