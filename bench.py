@@ -169,6 +169,8 @@ def build_model(device):
         model.use_fused = os.environ["Q40_FUSED"] != "0"
     if "Q40_PDL" in os.environ:
         model.use_pdl = os.environ["Q40_PDL"] != "0"
+    if "Q40_TILED" in os.environ:
+        model.use_tiled = os.environ["Q40_TILED"] != "0"
     if "Q40_FATTN" in os.environ:
         model.fused_attn_max_width = int(os.environ["Q40_FATTN"])
         model.use_fused_attn = model.fused_attn_max_width > 0

@@ -64,6 +64,11 @@ def _worker(rank, world, port, ret):
     with torch.inference_mode():
         tpm = _build(args, full, emb, out, rank, world, None)
         ref = _build(args, full, emb, out, 0, 1, None) if rank == 0 else None
+        if ref is not None:
+            # the tensor-parallel step runs the checkpoint-layout kernels one by one; give the one-GPU
+            # model the same kernels, so that only the sharding differs (the tiled decode kernels
+            # round scale * x instead of code * scale)
+            ref.use_fused = False
         g = torch.Generator().manual_seed(3)
         prompt = torch.randint(0, 256, (1, 17), generator=g).cuda()
         lt = tpm(prompt, 0)
