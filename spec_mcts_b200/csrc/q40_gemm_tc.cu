@@ -46,11 +46,14 @@ constexpr unsigned TC_SPIN_LIMIT = 1u << 22;   // polls of ~50 ns each before gi
 struct TcParams {
   const __half* a;      // [M, lda]
   int64_t lda;
-  const uint8_t* bw;    // [K, N/2]
-  const __half* bs;     // [K, N/64]
-  __half* c;            // [M, ldc]
-  int64_t ldc;
-  int M, N, K, Mpad, rows_per_split;
+  // up to three weight matrices that share the activations (wq, wk, wv): feature tiles of matrix 0
+  // first, then matrix 1, ...
+  const uint8_t* bw[3]; // [K, N/2]
+  const __half* bs[3];  // [K, N/64]
+  __half* c[3];         // [M, ldc]
+  int64_t ldc[3];
+  int N[3], tiles[3], nprob;
+  int M, K, Mpad, rows_per_split;
   int* err;             // device word, set non-zero when a bounded wait expired
   void* trace;          // stage timestamps (trace builds only)
 };
@@ -119,7 +122,9 @@ gemm_tc_kernel(const TcParams p) {
   extern __shared__ unsigned char tc_smem_raw[];
   cg::cluster_group cluster = cg::this_cluster();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int tile = blockIdx.x, split = blockIdx.y;
+  int pi = 0, tile = blockIdx.x;
+  while (pi < p.nprob - 1 && tile >= p.tiles[pi]) { tile -= p.tiles[pi]; ++pi; }
+  const int split = blockIdx.y;
   Q40_TRACE_DECL
   Q40_STAMP(0);
   const int kb = split * p.rows_per_split;
@@ -173,9 +178,9 @@ gemm_tc_kernel(const TcParams p) {
     // k row gt / TPR of every block
     const int grp = tid / GT, gt = tid % GT;
     const int kr = gt / TPR, q0 = (gt % TPR) * NQ;
-    const int64_t w_ld = p.N / 2, s_ld = p.N / 64;
-    const uint8_t* wp = p.bw + (int64_t)(kb + kr) * w_ld + tile * 64 + 16 * q0;
-    const __half* sp = p.bs + (int64_t)(kb + kr) * s_ld + tile * 2;
+    const int64_t w_ld = p.N[pi] / 2, s_ld = p.N[pi] / 64;
+    const uint8_t* wp = p.bw[pi] + (int64_t)(kb + kr) * w_ld + tile * 64 + 16 * q0;
+    const __half* sp = p.bs[pi] + (int64_t)(kb + kr) * s_ld + tile * 2;
     const uint32_t my_ring = ring_u32 + grp * 2 * RAW_SLOT;
     unsigned char* my_ring_g = ring + grp * 2 * RAW_SLOT;
     // raw weights of block blk into ring slot `rs`: piece q of row kr at [q][kr] (conflict-free reads)
@@ -320,8 +325,8 @@ gemm_tc_kernel(const TcParams p) {
 #pragma unroll
       for (int r = 0; r < 8; ++r) { v.x += t[r].x; v.y += t[r].y; v.z += t[r].z; v.w += t[r].w; }
       const int m = e / TC_TILE_N, n = tile * TC_TILE_N + e % TC_TILE_N;      // four features of one row
-      if (n + 3 < p.N) {
-        __half2* dst = reinterpret_cast<__half2*>(p.c + (int64_t)m * p.ldc + n);
+      if (n + 3 < p.N[pi]) {
+        __half2* dst = reinterpret_cast<__half2*>(p.c[pi] + (int64_t)m * p.ldc[pi] + n);
         dst[0] = __floats2half2_rn(v.x, v.y);
         dst[1] = __floats2half2_rn(v.z, v.w);
       }
@@ -375,25 +380,35 @@ static int tc_max_clusters(TcKernel kern, int mpad, int nsplit, size_t smem) {
 // C[M,N] = A[M,K] @ deq(B)[K,N] for 16 < M, group 64, K % 64 == 0, N % 128 == 0, on tcgen05.
 // `err` is a device int the kernel sets to 1 if one of its bounded waits expires (results are then
 // undefined); the caller zeroes it beforehand and may read it after synchronising.
-extern "C" int q40_gemm_kn_tc(const void* a, int64_t lda, const void* bw, const void* bs, void* c,
-                              int64_t ldc, int M, int N, int K, int* err, void* stream) {
+extern "C" int q40_gemm_kn_tc_multi(int nmat, const void* a, int64_t lda, const void* const* bw,
+                                    const void* const* bs, void* const* c, const int64_t* ldc, const int* n_cols,
+                                    int M, int K, int* err, void* stream) {
   using namespace q40;
-  if (!a || !bw || !bs || !c || !err) return Q40_E_NULL;
-  if (M < 1 || N <= 0 || K <= 0 || N % 128 != 0 || K % TC_BK != 0) return Q40_E_SHAPE;
-  if (lda < K || ldc < N || lda % 8 != 0 || ldc % 2 != 0) return Q40_E_SHAPE;
-  if (!q40_aligned(a, 16) || !q40_aligned(bw, 16) || !q40_aligned(bs, 4)) return Q40_E_ALIGN;
+  if (!a || !bw || !bs || !c || !ldc || !n_cols || !err) return Q40_E_NULL;
+  if (nmat < 1 || nmat > 3) return Q40_E_UNSUPPORTED;
+  if (M < 1 || K <= 0 || K % TC_BK != 0 || lda < K || lda % 8 != 0) return Q40_E_SHAPE;
+  if (!q40_aligned(a, 16)) return Q40_E_ALIGN;
+  int tiles = 0;
+  for (int i = 0; i < nmat; ++i) {
+    if (!bw[i] || !bs[i] || !c[i]) return Q40_E_NULL;
+    if (n_cols[i] <= 0 || n_cols[i] % 128 != 0 || ldc[i] < n_cols[i] || ldc[i] % 2 != 0) return Q40_E_SHAPE;
+    if (!q40_aligned(bw[i], 16) || !q40_aligned(bs[i], 4) || !q40_aligned(c[i], 4)) return Q40_E_ALIGN;
+    tiles += n_cols[i] / TC_TILE_N;
+  }
   cudaStream_t st = (cudaStream_t)stream;
-  const int tiles = N / TC_TILE_N;
   const int kblocks = K / TC_BK;
   const __half* ah = (const __half*)a;
-  __half* ch = (__half*)c;
   for (int m0 = 0; m0 < M; m0 += 256) {
     const int mc = (M - m0) < 256 ? (M - m0) : 256;
     TcParams p{};
     p.a = ah + (int64_t)m0 * lda; p.lda = lda;
-    p.bw = (const uint8_t*)bw; p.bs = (const __half*)bs;
-    p.c = ch + (int64_t)m0 * ldc; p.ldc = ldc;
-    p.M = mc; p.N = N; p.K = K; p.Mpad = (mc + 15) / 16 * 16;
+    p.nprob = nmat;
+    for (int i = 0; i < nmat; ++i) {
+      p.bw[i] = (const uint8_t*)bw[i]; p.bs[i] = (const __half*)bs[i];
+      p.c[i] = (__half*)c[i] + (int64_t)m0 * ldc[i]; p.ldc[i] = ldc[i];
+      p.N[i] = n_cols[i]; p.tiles[i] = n_cols[i] / TC_TILE_N;
+    }
+    p.M = mc; p.K = K; p.Mpad = (mc + 15) / 16 * 16;
     p.err = err;
 #ifdef Q40_TRACE
     p.trace = q40_trace_ptr;
@@ -436,4 +451,9 @@ extern "C" int q40_gemm_kn_tc(const void* a, int64_t lda, const void* bw, const 
     if (e != cudaSuccess) return (int)e;
   }
   return Q40_OK;
+}
+
+extern "C" int q40_gemm_kn_tc(const void* a, int64_t lda, const void* bw, const void* bs, void* c,
+                              int64_t ldc, int M, int N, int K, int* err, void* stream) {
+  return q40_gemm_kn_tc_multi(1, a, lda, &bw, &bs, &c, &ldc, &N, M, K, err, stream);
 }

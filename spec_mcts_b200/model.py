@@ -315,6 +315,26 @@ class Transformer(nn.Module):
                               out.stride(0), x.shape[0], N, Kd, lin.group_size, ws.data_ptr(), ws.numel(), st),
               "q40_gemm_kn")
 
+    def _gemm_multi(self, bufs, x, lins, outs, st):
+        """Several projections of the same activations: one tensor-core launch above 16 rows when the
+        shapes allow it, one launch per matrix otherwise."""
+        import ctypes
+        M, n = x.shape[0], len(lins)
+        ok = M > 16 and n <= 3 and all(l.group_size == 64 and l.kn()[1] % 128 == 0 and l.kn()[0] % 64 == 0 and
+                                       l.kn()[0] == lins[0].kn()[0] and o.stride(0) % 2 == 0
+                                       for l, o in zip(lins, outs)) and x.stride(0) % 8 == 0
+        if not ok:
+            for l, o in zip(lins, outs):
+                self._gemm(bufs, x, l, o, st)
+            return
+        P = ctypes.c_void_p * n
+        err = bufs["gemm_ws"].data_ptr() + 4096 - 4      # the error word q40_gemm_kn also uses
+        check(lib.q40_gemm_kn_tc_multi(n, x.data_ptr(), x.stride(0), P(*[l.w.data_ptr() for l in lins]),
+                                       P(*[l.s.data_ptr() for l in lins]), P(*[o.data_ptr() for o in outs]),
+                                       (ctypes.c_int64 * n)(*[o.stride(0) for o in outs]),
+                                       (ctypes.c_int * n)(*[l.kn()[1] for l in lins]), M, lins[0].kn()[0], err, st),
+              "q40_gemm_kn_tc_multi")
+
     def _decode_body(self, B):
         """Enqueue one decode step for B branches on the current stream (captured into a graph)."""
         if self.use_megakernel and B <= 8 and self.tp_world == 1:
@@ -472,9 +492,7 @@ class Transformer(nn.Module):
         for layer in self.layers:
             att, ff = layer.attention, layer.feed_forward
             self._norm(h, pending, layer.attention_norm.weight, xn, st)
-            self._gemm(bufs, xn, att.wq, bufs["q"], st)
-            self._gemm(bufs, xn, att.wk, bufs["k"], st)
-            self._gemm(bufs, xn, att.wv, bufs["v"], st)
+            self._gemm_multi(bufs, xn, [att.wq, att.wk, att.wv], [bufs["q"], bufs["k"], bufs["v"]], st)
             check(lib.q40_rope_kv_append(bufs["q"].data_ptr(), H * D, bufs["k"].data_ptr(), Hkv * D,
                                          bufs["v"].data_ptr(), Hkv * D, pos.data_ptr(), plen.data_ptr(),
                                          self._cos.data_ptr(), self._sin.data_ptr(), self._n_pos,

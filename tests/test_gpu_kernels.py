@@ -166,6 +166,36 @@ def test_linear_nk_vs_oracle(K, M, NK, G):
     assert_close(host(y), O.linear_q40_nk(x, q, s, (N, Kd), G))
 
 
+@pytest.mark.parametrize("M", [17, 100, 300])
+def test_matmul_tc_multi_matches_oracle(K, M):
+    """Three matrices that share the activations in one tensor-core launch (the q, k, v projections
+    of a wide decode step), written into slices of one buffer with a common row pitch."""
+    import ctypes
+    from spec_mcts_b200._lib import check, lib
+    rng = np.random.default_rng(40 + M)
+    Kd, Ns = 512, (256, 128, 384)
+    a = (rng.standard_normal((M, Kd)) * 0.5).astype(np.float16)
+    mats = []
+    for n in Ns:
+        w = (rng.standard_normal((Kd, n)) * 0.3).astype(np.float16)
+        mats.append(O.quantize_q40(w, 64))
+    a_d = dev(a)
+    dm = [(dev(q), dev(s)) for q, s in mats]
+    out = torch.zeros((M, sum(Ns)), dtype=torch.float16, device="cuda")
+    views, c0 = [], 0
+    for n in Ns:
+        views.append(out[:, c0:c0 + n]); c0 += n
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    P = ctypes.c_void_p * 3
+    check(lib.q40_gemm_kn_tc_multi(3, a_d.data_ptr(), Kd, P(*[q.data_ptr() for q, _ in dm]),
+                                   P(*[s.data_ptr() for _, s in dm]), P(*[v.data_ptr() for v in views]),
+                                   (ctypes.c_int64 * 3)(*[out.stride(0)] * 3), (ctypes.c_int * 3)(*Ns), M, Kd,
+                                   err.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    assert int(err.item()) == 0
+    for v, (q, s), n in zip(views, mats, Ns):
+        assert_close(host(v), O.matmul_q40(a, q, s, (Kd, n)))
+
+
 def test_matmul_7b_shapes_linearity_and_repeatability(K):
     """Full CodeLlama-7B layer shapes: checked through properties that need no CPU matmul —
     (a) a one-hot activation row selects exactly the dequantised weight row, (b) repeated
