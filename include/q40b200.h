@@ -91,11 +91,13 @@ int q40_gemm_kn_tc(const void* a, int64_t lda, const void* bw, const void* bs, v
 /* q40_gemm_kn_tc for up to three weight matrices that share the activations and K (wq, wk, wv of a
  * layer) in one launch: the feature tiles of all matrices form one grid, so that small matrices
  * do not pay a launch each.  bw/bs/c/ldc/n_cols are host arrays of nmat entries read during the
- * call; every n_cols[i] % 128 == 0 and ldc[i] even.  No counterpart in the reference (its model
+ * call; every n_cols[i] % 128 == 0 and ldc[i] even.  use_pdl != 0 launches with programmatic stream
+ * serialization: the first weight blocks are requested while the previous launch on the stream
+ * drains, so that launch must not be the one that writes the weights.  No counterpart in the reference (its model
  * issues one matmul_q40 per projection, hf_model_q40_kv_shared.py:313-315). */
 int q40_gemm_kn_tc_multi(int nmat, const void* a, int64_t lda, const void* const* bw,
                          const void* const* bs, void* const* c, const int64_t* ldc, const int* n_cols,
-                         int M, int K, int* err, void* stream);
+                         int M, int K, int* err, int use_pdl, void* stream);
 
 /* q40_gemm_kn without a caller-provided workspace, for hosts that cannot allocate device
  * memory themselves (all HBM already handed to their own planner, or a plug-in that only

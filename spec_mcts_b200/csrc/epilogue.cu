@@ -82,6 +82,7 @@ rope_kernel(__half* __restrict__ x, const int32_t* __restrict__ pos, const __hal
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const __half* __restrict__ a, const __half* __restrict__ b, __half* __restrict__ y,
                 int64_t n) {
+  asm volatile("griddepcontrol.launch_dependents;");   // a dependent may start prefetching its weights
   const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i >= n) return;
   if (i + 8 <= n) {

@@ -166,6 +166,7 @@ gemm_tc_kernel(const TcParams p) {
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
+  asm volatile("griddepcontrol.launch_dependents;");
   Q40_STAMP(1);
 
   // instruction descriptor: D fp32, A/B fp16, A MN-major, B K-major, N = Mpad, M = 128
@@ -209,7 +210,11 @@ gemm_tc_kernel(const TcParams p) {
                      "l"(ok ? src + (int64_t)(GT / 8) * j * p.lda : p.a), "r"(sz));
       }
     };
-    if (grp < nblk) { issue_raw(grp, 0); issue_b(grp); }
+    // the weights do not depend on the previous launch: their first block is requested before this
+    // launch waits for it (programmatic dependent launch), the activations after
+    if (grp < nblk) issue_raw(grp, 0);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (grp < nblk) issue_b(grp);
     asm volatile("cp.async.commit_group;");
     unsigned char* a_st = gbase + grp * TC_A_BYTES;
     for (int k = 0, blk = grp; blk < nblk; ++k, blk += G) {
@@ -255,6 +260,7 @@ gemm_tc_kernel(const TcParams p) {
     // ================= the MMA warp: lane 0 issues, the warp stays converged =================
     // descriptors of A stage 0 / B slot 0; the others differ only in the 16-byte-granular start address
     // field (the low 14 bits; all of shared memory is below 256 KB, so the additions cannot carry out)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint64_t ad_base = tc_desc(base, 1024, 2048);          // A: two k groups per MMA
     const uint64_t bd_base = tc_desc(b_base, 16, 1024);          // B: 16 k = 32 bytes along the row
     for (int i = 0; i < nblk; ++i) {
@@ -382,7 +388,7 @@ static int tc_max_clusters(TcKernel kern, int mpad, int nsplit, size_t smem) {
 // undefined); the caller zeroes it beforehand and may read it after synchronising.
 extern "C" int q40_gemm_kn_tc_multi(int nmat, const void* a, int64_t lda, const void* const* bw,
                                     const void* const* bs, void* const* c, const int64_t* ldc, const int* n_cols,
-                                    int M, int K, int* err, void* stream) {
+                                    int M, int K, int* err, int use_pdl, void* stream) {
   using namespace q40;
   if (!a || !bw || !bs || !c || !ldc || !n_cols || !err) return Q40_E_NULL;
   if (nmat < 1 || nmat > 3) return Q40_E_UNSUPPORTED;
@@ -440,13 +446,15 @@ extern "C" int q40_gemm_kn_tc_multi(int nmat, const void* a, int64_t lda, const 
     cfg.blockDim = dim3(TC_BLOCK, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = nsplit;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = use_pdl ? 2 : 1;
     e = cudaLaunchKernelEx(&cfg, kern, p);
     if (e != cudaSuccess) return (int)e;
   }
@@ -455,5 +463,5 @@ extern "C" int q40_gemm_kn_tc_multi(int nmat, const void* a, int64_t lda, const 
 
 extern "C" int q40_gemm_kn_tc(const void* a, int64_t lda, const void* bw, const void* bs, void* c,
                               int64_t ldc, int M, int N, int K, int* err, void* stream) {
-  return q40_gemm_kn_tc_multi(1, a, lda, &bw, &bs, &c, &ldc, &N, M, K, err, stream);
+  return q40_gemm_kn_tc_multi(1, a, lda, &bw, &bs, &c, &ldc, &N, M, K, err, 0, stream);
 }

@@ -332,7 +332,8 @@ class Transformer(nn.Module):
         check(lib.q40_gemm_kn_tc_multi(n, x.data_ptr(), x.stride(0), P(*[l.w.data_ptr() for l in lins]),
                                        P(*[l.s.data_ptr() for l in lins]), P(*[o.data_ptr() for o in outs]),
                                        (ctypes.c_int64 * n)(*[o.stride(0) for o in outs]),
-                                       (ctypes.c_int * n)(*[l.kn()[1] for l in lins]), M, lins[0].kn()[0], err, st),
+                                       (ctypes.c_int * n)(*[l.kn()[1] for l in lins]), M, lins[0].kn()[0], err,
+                                       1 if self.use_pdl else 0, st),
               "q40_gemm_kn_tc_multi")
 
     def _decode_body(self, B):
@@ -507,14 +508,14 @@ class Transformer(nn.Module):
                                            pos.data_ptr(), bufs["k"].data_ptr(), bufs["v"].data_ptr(), Hkv * D,
                                            bufs["ao"].data_ptr(), B, H, Hkv, D, aws.data_ptr(), aws.numel(), st),
                   "q40_attn_tree_decode")
-            self._gemm(bufs, bufs["ao"], att.wo, bufs["o"], st)
+            self._gemm_multi(bufs, bufs["ao"], [att.wo], [bufs["o"]], st)
             self._all_reduce(bufs["o"])
             self._norm(h, bufs["o"], layer.ffn_norm.weight, xn, st)
-            self._gemm(bufs, xn, ff.w1, bufs["a1"], st)
-            self._gemm(bufs, xn, ff.w3, bufs["a3"], st)
+            self._gemm_multi(bufs, xn, [ff.w1], [bufs["a1"]], st)
+            self._gemm_multi(bufs, xn, [ff.w3], [bufs["a3"]], st)
             check(lib.q40_silu_mul(bufs["a1"].data_ptr(), bufs["a3"].data_ptr(), bufs["g"].data_ptr(),
                                    bufs["g"].numel(), st), "q40_silu_mul")
-            self._gemm(bufs, bufs["g"], ff.w2, bufs["f"], st)
+            self._gemm_multi(bufs, bufs["g"], [ff.w2], [bufs["f"]], st)
             self._all_reduce(bufs["f"])
             pending = bufs["f"]
         self._norm(h, pending, self.norm.weight, xn, st)

@@ -190,7 +190,7 @@ def test_matmul_tc_multi_matches_oracle(K, M):
     check(lib.q40_gemm_kn_tc_multi(3, a_d.data_ptr(), Kd, P(*[q.data_ptr() for q, _ in dm]),
                                    P(*[s.data_ptr() for _, s in dm]), P(*[v.data_ptr() for v in views]),
                                    (ctypes.c_int64 * 3)(*[out.stride(0)] * 3), (ctypes.c_int * 3)(*Ns), M, Kd,
-                                   err.data_ptr(), torch.cuda.current_stream().cuda_stream))
+                                   err.data_ptr(), 1, torch.cuda.current_stream().cuda_stream))
     assert int(err.item()) == 0
     for v, (q, s), n in zip(views, mats, Ns):
         assert_close(host(v), O.matmul_q40(a, q, s, (Kd, n)))
