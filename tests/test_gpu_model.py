@@ -176,7 +176,7 @@ def test_fork_copies_suffix_cache(small):
     assert int(model._prefix_len_dev.item()) == 0
 
 
-def test_convert_state_dict_matches_oracle_packer_and_loads(K):
+def test_convert_state_dict_matches_oracle_packer_and_loads(small):
     """The device-side converter: every projection packed exactly as the oracle (= the reference's
     torch packer) packs `W.t()`, other tensors untouched, and a model loaded from the result
     decodes like one loaded from the golden Q4_0 tensors."""
