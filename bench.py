@@ -169,6 +169,8 @@ def build_model(device):
         model.use_fused = os.environ["Q40_FUSED"] != "0"
     if "Q40_PDL" in os.environ:
         model.use_pdl = os.environ["Q40_PDL"] != "0"
+    if os.environ.get("Q40_LMHEAD_Q4", "0") != "0":
+        model.quantize_lm_head()      # not the reference's model: experiment only
     if "Q40_TILED" in os.environ:
         model.use_tiled = os.environ["Q40_TILED"] != "0"
     if "Q40_FATTN" in os.environ:

@@ -221,6 +221,7 @@ class Transformer(nn.Module):
         self.use_fused_attn = True
         self.fused_attn_max_width = 1
         self._layer_table = None
+        self._lm_head_q4 = None     # set by quantize_lm_head()
         self._trace = None       # optional int64 tensor [6 * n_layers + 8]: barrier timestamps of the step kernel
 
     # ------------------------------------------------------------------ reference API
@@ -430,12 +431,39 @@ class Transformer(nn.Module):
                         ss_in=ss_attn, ss_in_count=c_attn, st=st)
             self._fused(2, [ff.w2], [h], p.dim, gbuf, hid, B, h_in=h, ldh=p.dim, ss_out=ss_ffn,
                         ss_out_count=c_ffn, st=st)
-        self._norm(h, None, self.norm.weight, bufs["xn"], st)
-        torch.matmul(bufs["xn"], self.output.weight.t(), out=bufs["logits"])
+        if self._lm_head_q4 is not None:
+            # final RMSNorm as the prologue of the Q4_0 lm_head launch; the padded columns are cut off
+            lin = self._lm_head_q4
+            vp = lin.kn()[1]
+            if "logits_pad" not in bufs:
+                bufs["logits_pad"] = torch.empty((B, vp), dtype=DTYPE, device=self.device)
+            self._fused(1, [lin], [bufs["logits_pad"]], vp, h, p.dim, B, norm_w=self.norm.weight, ss_in=ss_ffn,
+                        ss_in_count=c_ffn, st=st)
+            logits = bufs["logits_pad"][:, :p.vocab_size]
+        else:
+            self._norm(h, None, self.norm.weight, bufs["xn"], st)
+            logits = bufs["logits"]
+            torch.matmul(bufs["xn"], self.output.weight.t(), out=logits)
         if self.greedy_feedback:
-            self._tok_dev[:B].copy_(bufs["logits"].argmax(dim=-1))
+            self._tok_dev[:B].copy_(logits.argmax(dim=-1))
             self._pos_dev[:B] += 1
-        return bufs["logits"]
+        return logits
+
+    def quantize_lm_head(self):
+        """Optional, and NOT the reference's model (its lm_head stays fp16, so logits change by the
+        quantisation error): pack `output.weight` as Q4_0 (vocabulary padded to a multiple of 256 with
+        zero rows) and let decode steps of up to 16 branches compute final RMSNorm + lm_head in one
+        tiled matmul launch.  Wider steps and the prompt pass keep the fp16 weight."""
+        W = self.output.weight
+        V, dim = W.shape
+        vp = (V + 255) // 256 * 256
+        wp = torch.zeros((vp, dim), dtype=DTYPE, device=W.device)
+        wp[:V] = W.to(DTYPE)
+        lin = LinearQ4_0(dim, vp, GROUP_SIZE)
+        lin.w, lin.s = K.quantize_q40(wp.t().contiguous(), GROUP_SIZE)
+        lin.shape = (vp, dim)
+        self._lm_head_q4 = lin
+        self._graphs.clear()
 
     def _build_layer_table(self):
         """Device array of per-layer pointer records in the order q40_decode_step documents."""
@@ -591,6 +619,8 @@ class Transformer(nn.Module):
                 # (capture itself executes nothing)
                 self._pos_dev[:B] -= 1
         g.replay()
+        if self._lm_head_q4 is not None and fused and not mega:
+            return self._bufs[B]["logits_pad"][:, :self.params.vocab_size]
         return self._bufs[B]["logits"]
 
 

@@ -212,3 +212,28 @@ def test_convert_state_dict_matches_oracle_packer_and_loads(small):
     with torch.inference_mode():
         logits = model(torch.arange(9).view(1, 9).cuda(), 0)
     assert logits.shape[-1] == 512 and torch.isfinite(logits.float()).all()
+
+
+def test_q4_lm_head_option(small):
+    """The optional Q4_0 lm_head (final RMSNorm + lm_head in one tiled launch): logits equal the
+    stand-alone Q4_0 matmul of the normalised hidden state, and the fp16 head is untouched for the
+    prompt pass."""
+    from spec_mcts_b200 import kernels as KK
+    model = build_model(small, True)
+    prompt = torch.from_numpy(small["prompt"]).cuda()
+    with torch.inference_mode():
+        model(prompt, 0)
+        model.fork(0, 1, 2)
+        toks = torch.from_numpy(small["first_tokens"]).cuda()
+        pos = prompt.shape[1]
+        ref = model(toks, pos)[:, -1].float().clone()            # fp16 head
+        model.quantize_lm_head()
+        # same position again: the cache row is rewritten with the same values
+        got = model(toks, pos)[:, -1].float()
+        lin = model._lm_head_q4
+        xn = model._step_buffers(3)["xn"]                           # written by the fp16-head step above
+        want = KK.matmul_q40(xn[:3].contiguous(), lin.w, lin.s, lin.kn())[:, :got.shape[-1]].float()
+    np.testing.assert_allclose(got.cpu().numpy(), want.cpu().numpy(), rtol=2e-2, atol=2e-2)
+    # and it is a quantised version of the fp16 head, not something else
+    rel = float((got - ref).norm() / ref.norm())
+    assert rel < 0.2, rel
