@@ -376,6 +376,121 @@ def run_70b_tp(args):
         os._exit(0)
 
 
+def run_kernel_sweep(args):
+    """`--workload kernels`: the stand-alone kernels on the benchmark's kernel-level configurations,
+    one JSON line.  (1, 2) Q4_0 matmul over the 7B layer shapes at M = 1, 10, 100: every call of a
+    timed pass uses a different weight matrix (16 distinct ones, > 126 MB in total for each shape),
+    so the figures are HBM figures, not L2 ones; the pass is replayed from a CUDA graph.  For M <= 16
+    both the checkpoint-layout entry (`matmul_q40`) and the decode step's tiled stream are timed.
+    (3) shared-prefix tree attention: 2048 shared prompt keys, 64 branches with suffixes of 0..256
+    tokens in 16-token pages."""
+    import numpy as np
+    import torch
+    from spec_mcts_b200 import kernels as K
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    tf_peak = float(peaks.get("bf16_tflops", 1590.0))
+    g = torch.Generator(device=dev).manual_seed(0)
+    NW = 16
+
+    def timed(fn, reps=20):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize(dev)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            fn()
+        for _ in range(3):
+            gr.replay()
+        torch.cuda.synchronize(dev)
+        ts = []
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            gr.replay()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            ts.append(e0.elapsed_time(e1) * 1e-3)
+        ts.sort()
+        return ts[len(ts) // 2], ts[len(ts) // 5], ts[4 * len(ts) // 5]
+
+    rows = []
+    for (N, Kd) in ((4096, 4096), (11008, 4096), (4096, 11008), (32128, 4096)):
+        ws = []
+        for i in range(NW):
+            w = (torch.randn((Kd, N), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.float16)
+            q, sc = K.quantize_q40(w, 64)
+            ws.append((q, sc))
+            del w
+        tiled = [K.relayout_tiled(q, sc, (Kd, N)) for q, sc in ws] if N % 256 == 0 else None
+        for M in (1, 10, 100):
+            a = torch.randn((M, Kd), generator=g, device=dev, dtype=torch.float16)
+            byts = N * Kd * (0.5 + 2 / 64) + 2 * M * Kd + 2 * M * N
+            flops = 2.0 * M * N * Kd
+            variants = [("matmul_q40", lambda: [K.matmul_q40(a, q, sc, (Kd, N)) for q, sc in ws])]
+            if M <= 16 and tiled is not None:
+                variants.append(("gemv_tiled", lambda: [K.gemv_fused(0, a, [(t, None, (Kd, N))], tiled=True, use_pdl=True)
+                                                        for t in tiled]))
+            for name, fn in variants:
+                med, p20, p80 = timed(fn)
+                us = med / NW * 1e6
+                rows.append({"kernel": name, "N": N, "K": Kd, "M": M, "us": round(us, 2),
+                             "us_p20_p80": [round(p20 / NW * 1e6, 2), round(p80 / NW * 1e6, 2)],
+                             "GBs": round(byts / (med / NW) / 1e9, 1), "frac_hbm_measured": round(byts / (med / NW) / 1e9 / hbm, 3),
+                             "frac_hbm_8000": round(byts / (med / NW) / 1e9 / 8000.0, 3),
+                             "TFLOPs": round(flops / (med / NW) / 1e12, 2),
+                             "frac_bf16_measured": round(flops / (med / NW) / 1e12 / tf_peak, 4)})
+        del ws, tiled
+        torch.cuda.empty_cache()
+
+    # ---- configuration 3: shared-prefix tree attention ----
+    H, D, P0, B, page = 32, 128, 2048, 64, 16
+    rng = np.random.default_rng(0)
+    lens = rng.integers(0, 257, size=B)
+    npages = [(int(l) + page - 1) // page for l in lens]
+    tot_pages = int(sum(npages))
+    tbl = np.zeros((B, max(max(npages), 1)), dtype=np.int32)
+    nxt = 0
+    for b in range(B):
+        for j in range(npages[b]):
+            tbl[b, j] = nxt
+            nxt += 1
+    pk = torch.randn((P0, H, D), generator=g, device=dev, dtype=torch.float16)
+    pv = torch.randn((P0, H, D), generator=g, device=dev, dtype=torch.float16)
+    kpool = torch.randn((H, max(tot_pages, 1) * page, D), generator=g, device=dev, dtype=torch.float16)
+    vpool = torch.randn((H, max(tot_pages, 1) * page, D), generator=g, device=dev, dtype=torch.float16)
+    qq = torch.randn((B, H, D), generator=g, device=dev, dtype=torch.float16)
+    tbl_d = torch.from_numpy(tbl).to(dev)
+    lens_d = torch.from_numpy(lens.astype(np.int32)).to(dev)
+    # slot-granular table for the page-size-1 form the reference's page_flash_attn takes is not needed:
+    # the library's paged entry takes 16-token pages directly
+    med, p20, p80 = timed(lambda: K.shared_prefix_attn(qq, pk, pv, P0, tbl_d, lens_d, kpool, vpool, page_size=page))
+    prefix_bytes = 2 * P0 * H * D * 2
+    suffix_bytes = int(lens.sum()) * H * D * 2 * 2
+    alg = prefix_bytes + suffix_bytes + 2 * B * H * D * 2
+    naive = B * prefix_bytes + suffix_bytes
+    attn = {"prefix_len": P0, "branches": B, "suffix_tokens": int(lens.sum()), "page_size": page, "us": round(med * 1e6, 2),
+            "us_p20_p80": [round(p20 * 1e6, 2), round(p80 * 1e6, 2)], "algorithmic_bytes": alg,
+            "GBs": round(alg / med / 1e9, 1), "frac_hbm_measured": round(alg / med / 1e9 / hbm, 3),
+            "effective_kv_bytes_if_prefix_were_per_branch": naive,
+            "effective_GBs": round(naive / med / 1e9, 1), "effective_over_hbm_measured": round(naive / med / 1e9 / hbm, 2)}
+    print(json.dumps({"workload": "kernel-level configurations (Q4_0 matmul sweep, shared-prefix tree attention)",
+                      "peaks": {"hbm_gbs_measured": hbm, "hbm_gbs_nominal": 8000.0, "bf16_tflops_measured": tf_peak},
+                      "distinct_weight_buffers_per_pass": NW, "matmul": rows, "tree_attention": attn}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -387,10 +502,13 @@ def main():
     ap.add_argument("--skip-prefill", action="store_true",
                     help="profiling aid: fill the prompt cache with random K/V instead of running the prompt "
                          "(keeps a profiler capture short); not a valid benchmark configuration")
-    ap.add_argument("--workload", default="7b", choices=["7b", "70b-tp"])
+    ap.add_argument("--workload", default="7b", choices=["7b", "70b-tp", "kernels"])
     ap.add_argument("--tp-layers", type=int, default=80)
     ap.add_argument("--tp-branches", type=int, default=64)
     args = ap.parse_args()
+    if args.workload == "kernels" and args.impl != "reference":
+        run_kernel_sweep(args)
+        return
     if args.workload == "70b-tp" and args.impl != "reference":
         run_70b_tp(args)
         return

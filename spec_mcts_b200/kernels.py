@@ -169,12 +169,36 @@ def matmul_q40(a: torch.Tensor, b_w: torch.Tensor, b_s: torch.Tensor, b_shape, *
     c = out if out is not None else torch.empty((M, N), device=dev, dtype=torch.float16)
     if M == 0:
         return c
+    if (M <= 16 and group_size == 64 and N % 128 == 0 and K % 16 == 0 and K >= 64 and a.data_ptr() % 16 == 0
+            and c.stride(1) == 1 and _cluster_gemv(dev, a, b_w, b_s, c, M, N, K)):
+        return c
     nbytes = lib.q40_gemm_workspace_bytes(M, N, K)
     ws = _workspace("gemm", dev, nbytes, zero=True)
     check(lib.q40_gemm_kn(a.data_ptr(), a.stride(0), b_w.data_ptr(), b_s.data_ptr(), c.data_ptr(),
                           c.stride(0), M, N, K, group_size, ws.data_ptr(), ws.numel(), _stream(dev)),
           "q40_gemm_kn")
     return c
+
+
+_cluster_size = {}      # device index -> largest cluster the device schedules for the decode matmul (16 or 8)
+
+
+def _cluster_gemv(dev, a, b_w, b_s, c, M, N, K) -> bool:
+    """Up to 16 rows: the decode step's cluster-reduced kernel in its plain form (mode 0 of
+    q40_gemv_fused: no scratch, split-K summed through distributed shared memory), 2-4x faster than
+    the workspace kernel behind q40_gemm_kn.  False if the launch was refused for this shape."""
+    import ctypes
+    P = ctypes.c_void_p * 1
+    for cluster in ((_cluster_size.get(dev.index, 16),) if dev.index in _cluster_size else (16, 8)):
+        rc = lib.q40_gemv_fused(0, 1, P(b_w.data_ptr()), P(b_s.data_ptr()), P(c.data_ptr()), (ctypes.c_int * 1)(N),
+                                c.stride(0), a.data_ptr(), a.stride(0), M, K, None, None, 0, 0.0, None, 0, None, 0,
+                                cluster, 0, _stream(dev))
+        if rc == 0:
+            _cluster_size[dev.index] = cluster
+            return True
+        if rc > 0:
+            check(rc, "q40_gemv_fused")
+    return False
 
 
 def tc_error_flag(dev=None) -> int:
