@@ -72,6 +72,10 @@ size_t q40_gemm_workspace_bytes(int M, int N, int K);
 /* C[M,N] = A[M,K] @ deq(B)[K,N], B quantised from a row-major [K,N] matrix (groups along
  * N; the on-disk orientation): bw viewed as [K, N/2] bytes, bs as [K, N/group] fp16.
  * fp16 in, fp32 accumulate, fp16 out.  lda/ldc in elements.  N % (2*group) == 0.
+ * Up to 16 rows run a split-K kernel that sums its partials through the workspace (any shape);
+ * for group 64, N % 128 == 0 and K % 16 == 0 the cluster-reduced launch q40_gemv_fused (mode 0, one
+ * matrix) computes the same product without a workspace and 1.2-2x faster, and is what the Python
+ * matmul_q40 of this repository calls for such shapes.
  * Replaces: matmul_q40 (triton_kernels.py:357-500), called by LinearQ4_0.forward
  * (hf_model_q40_kv_shared.py:228-236). */
 int q40_gemm_kn(const void* a, int64_t lda, const void* bw, const void* bs, void* c,
