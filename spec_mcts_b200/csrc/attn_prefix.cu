@@ -256,7 +256,11 @@ static int prefix_splits(int B, int H, int Hkv, int prefix_len) {
   const int rows = B * rep;
   const int rblocks = (rows + 127) / 128;
   const int tiles = (prefix_len + PF_KT - 1) / PF_KT;
-  int want = (148 + Hkv * rblocks - 1) / (Hkv * rblocks);   // about one CTA per SM
+  // CTAs per SM to aim for: two for the 64-row variant (128 threads; measured best for 2048 keys x 64
+  // rows), one for the 128-row variant; never round up past whole waves (a 149th CTA doubles the time
+  // of one SM)
+  const int per_sm = rows <= 64 ? 2 : 1;
+  int want = (148 * per_sm) / (Hkv * rblocks);
   if (want < 1) want = 1;
   if (want > tiles) want = tiles;
   if (want < 1) want = 1;
@@ -289,7 +293,7 @@ extern "C" size_t q40_attn_shared_prefix_workspace_bytes(int B, int H, int D, in
   if (B <= 0 || H <= 0 || D != q40::ATTN_D || prefix_len <= 0) return 0;
   // the split count depends on Hkv; Hkv = 1 with 128-row blocks gives the largest count
   const int tiles = (prefix_len + q40::PF_KT - 1) / q40::PF_KT;
-  const int max_sp = tiles < 148 ? tiles : 148;
+  const int max_sp = tiles < 296 ? tiles : 296;
   return (size_t)max_sp * B * H * (D + 2) * sizeof(float);
 }
 
