@@ -46,6 +46,7 @@ __global__ void __launch_bounds__(BR_THREADS)
 attn_branch_kernel(const BranchArgs a) {
   constexpr int D = ATTN_D;
   asm volatile("griddepcontrol.launch_dependents;");   // a dependent may start prefetching its weights
+  asm volatile("griddepcontrol.wait;" ::: "memory");               // ... but nothing of the previous launch is read before it is done
   const int bh = blockIdx.x;
   const int b = bh / a.H, h = bh % a.H;
   const int hk = h / (a.H / a.Hkv);
@@ -274,11 +275,12 @@ attn_branch_kernel(const BranchArgs a) {
 
 int launch_branch(const BranchArgs& a, int mode, int B, cudaStream_t st) {
   const unsigned grid = (unsigned)(B * a.H);
-  if (mode == 0) attn_branch_kernel<0><<<grid, BR_THREADS, 0, st>>>(a);
-  else if (mode == 1) attn_branch_kernel<1><<<grid, BR_THREADS, 0, st>>>(a);
-  else if (mode == 2) attn_branch_kernel<2><<<grid, BR_THREADS, 0, st>>>(a);
-  else attn_branch_kernel<3><<<grid, BR_THREADS, 0, st>>>(a);
-  Q40_LAUNCH_CHECK();
+  cudaError_t e;
+  if (mode == 0) e = q40_launch_pdl(attn_branch_kernel<0>, dim3(grid), dim3(BR_THREADS), 0, st, a);
+  else if (mode == 1) e = q40_launch_pdl(attn_branch_kernel<1>, dim3(grid), dim3(BR_THREADS), 0, st, a);
+  else if (mode == 2) e = q40_launch_pdl(attn_branch_kernel<2>, dim3(grid), dim3(BR_THREADS), 0, st, a);
+  else e = q40_launch_pdl(attn_branch_kernel<3>, dim3(grid), dim3(BR_THREADS), 0, st, a);
+  if (e != cudaSuccess) return (int)e;
   return Q40_OK;
 }
 

@@ -86,6 +86,7 @@ attn_prefix_kernel(const PrefixArgs a) {
   // [stage][K tile | V tile]; the Q rows are staged through the same memory first
   const uint32_t sbase = smem_u32(smem);
   asm volatile("griddepcontrol.launch_dependents;");   // a dependent may start prefetching its weights
+  asm volatile("griddepcontrol.wait;" ::: "memory");               // ... but nothing of the previous launch is read before it is done
 
   const int sp = blockIdx.x, hk = blockIdx.y, rblk = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -277,13 +278,14 @@ static int launch_prefix(PrefixArgs& pa, int nsp, cudaStream_t st) {
   if (rows <= 64) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefix_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attn_prefix_kernel<4><<<dim3(nsp, pa.Hkv, 1), 128, smem, st>>>(pa);
+    e = q40_launch_pdl(attn_prefix_kernel<4>, dim3(nsp, pa.Hkv, 1), dim3(128), smem, st, pa);
+    if (e != cudaSuccess) return (int)e;
   } else {
     cudaError_t e = cudaFuncSetAttribute(attn_prefix_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attn_prefix_kernel<8><<<dim3(nsp, pa.Hkv, (rows + 127) / 128), 256, smem, st>>>(pa);
+    e = q40_launch_pdl(attn_prefix_kernel<8>, dim3(nsp, pa.Hkv, (rows + 127) / 128), dim3(256), smem, st, pa);
+    if (e != cudaSuccess) return (int)e;
   }
-  Q40_LAUNCH_CHECK();
   return Q40_OK;
 }
 

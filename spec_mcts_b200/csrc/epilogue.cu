@@ -14,6 +14,7 @@ rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ residual
   __half* row = reinterpret_cast<__half*>(smem_raw);  // [dim]
   __shared__ float red[8];
   asm volatile("griddepcontrol.launch_dependents;");   // a dependent may start prefetching its weights
+  asm volatile("griddepcontrol.wait;" ::: "memory");               // ... but nothing of the previous launch is read before it is done
   const int r = blockIdx.x, tid = threadIdx.x;
   const __half* xr = x + (int64_t)r * dim;
   const __half* rr = residual ? residual + (int64_t)r * dim : nullptr;
@@ -83,6 +84,7 @@ __global__ void __launch_bounds__(256)
 silu_mul_kernel(const __half* __restrict__ a, const __half* __restrict__ b, __half* __restrict__ y,
                 int64_t n) {
   asm volatile("griddepcontrol.launch_dependents;");   // a dependent may start prefetching its weights
+  asm volatile("griddepcontrol.wait;" ::: "memory");               // ... but nothing of the previous launch is read before it is done
   const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i >= n) return;
   if (i + 8 <= n) {
@@ -167,9 +169,10 @@ extern "C" int q40_rmsnorm(const void* x, const void* residual, const void* w, v
                                          (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  q40::rmsnorm_kernel<<<rows, 256, smem, (cudaStream_t)stream>>>(
-      (const __half*)x, (const __half*)residual, (const __half*)w, (__half*)y, (__half*)h_out, dim, eps);
-  Q40_LAUNCH_CHECK();
+  const cudaError_t e2 = q40_launch_pdl(q40::rmsnorm_kernel, dim3(rows), dim3(256), smem, (cudaStream_t)stream,
+                                        (const __half*)x, (const __half*)residual, (const __half*)w, (__half*)y,
+                                        (__half*)h_out, dim, eps);
+  if (e2 != cudaSuccess) return (int)e2;
   return Q40_OK;
 }
 
@@ -196,8 +199,8 @@ extern "C" int q40_silu_mul(const void* a, const void* b, void* y, int64_t n, vo
   const int64_t threads = (n + 7) / 8;
   const int64_t grid = (threads + 255) / 256;
   if (grid > 0x7fffffffLL) return Q40_E_SHAPE;
-  q40::silu_mul_kernel<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>((const __half*)a, (const __half*)b,
-                                                                        (__half*)y, n);
-  Q40_LAUNCH_CHECK();
+  const cudaError_t e = q40_launch_pdl(q40::silu_mul_kernel, dim3((unsigned)grid), dim3(256), 0, (cudaStream_t)stream,
+                                       (const __half*)a, (const __half*)b, (__half*)y, n);
+  if (e != cudaSuccess) return (int)e;
   return Q40_OK;
 }

@@ -50,6 +50,7 @@ rope_kv_append_kernel(const AppendArgs a) {
   constexpr int D = 128, HD = 64;
   __shared__ float red[2];
   asm volatile("griddepcontrol.launch_dependents;");   // a dependent may start prefetching its weights
+  asm volatile("griddepcontrol.wait;" ::: "memory");               // ... but nothing of the previous launch is read before it is done
   const int b = blockIdx.x, hh = blockIdx.y, d = threadIdx.x;
   int p = a.pos[b];
   p = min(max(p, 0), a.n_pos - 1);
@@ -115,7 +116,7 @@ extern "C" int q40_rope_kv_append(void* q, int64_t q_stride, void* k, int64_t k_
   a.cache_kq = (int8_t*)cache_kq; a.cache_ks = (__half*)cache_ks;
   a.cache_vq = (int8_t*)cache_vq; a.cache_vs = (__half*)cache_vs;
   a.H = H; a.Hkv = Hkv; a.max_t = max_t; a.n_pos = n_pos;
-  q40::rope_kv_append_kernel<<<dim3(B, H + Hkv), 64, 0, (cudaStream_t)stream>>>(a);
-  Q40_LAUNCH_CHECK();
+  const cudaError_t e = q40_launch_pdl(q40::rope_kv_append_kernel, dim3(B, H + Hkv), dim3(64), 0, (cudaStream_t)stream, a);
+  if (e != cudaSuccess) return (int)e;
   return Q40_OK;
 }

@@ -18,6 +18,27 @@
 
 static inline bool q40_aligned(const void* p, size_t a) { return ((uintptr_t)p % a) == 0; }
 
+// Launch with programmatic stream serialization.  Kernels launched this way execute griddepcontrol.wait
+// before their first access to global memory, so for the caller the launch orders exactly like a plain
+// one; what changes is that the CTAs may become resident while the previous launch on the stream drains
+// (and, where that launch triggered early, while it runs), which takes the launch latency off the
+// critical path of a chain of small dependent launches.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t q40_launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                         cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 // Optional stage timestamps (builds with -DQ40_TRACE only; compiled out otherwise): thread 0 of a CTA
 // reads the global nanosecond timer at up to 8 points and appends one record of 10 words
 // {kind, linear CTA id, t0..t7} to the buffer given to q40_debug_trace (word 0 = record counter,
