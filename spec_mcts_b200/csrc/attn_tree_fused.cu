@@ -1,7 +1,7 @@
 // Decode attention of the KV-shared model as ONE launch: rotary embedding of q and of the new key,
 // Q4_0 append of the new key/value, and attention over [shared fp16 prompt | packed Q4_0 suffix |
 // the un-quantised new token].  A thread-block cluster of 8 CTAs serves one (branch, head): its
-// 256 groups of 8 lanes take the keys round-robin (each lane owns 16 of the 128 head dims), every
+// 128 groups of 8 lanes take the keys round-robin (each lane owns 16 of the 128 head dims), every
 // group keeps an fp32 online-softmax state, groups are merged through shared memory inside a
 // CTA and the CTAs through distributed shared memory, each rank finishing 16 output dims.
 // Meant for small widths (up to about 16 branches), where three separate launches (rotary+append,
@@ -18,9 +18,10 @@ namespace cg = cooperative_groups;
 
 namespace q40 {
 
-constexpr int TF_THREADS = 256;
+constexpr int TF_THREADS = 128;
+constexpr int TF_WARPS = TF_THREADS / 32;
 constexpr int TF_CLUSTER = 8;
-constexpr int TF_KPG = 3;          // keys a group of 8 lanes holds in registers per batch (768 per cluster)
+constexpr int TF_KPG = 5;          // keys a group of 8 lanes holds in registers per batch (640 per cluster)
 
 struct TreeFusedArgs {
   __half* qkv;             // [B, W]: q heads, then k heads, then v heads of the new token (un-rotated)
@@ -105,8 +106,8 @@ attn_tree_fused_kernel(const TreeFusedArgs a) {
   // phase 1 of the cluster barrier only says "this CTA is running" (waited for before the first
   // store into a neighbour's shared memory); phase 2 publishes those stores
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  __shared__ float cta_m[8], cta_l[8];
-  __shared__ __align__(16) float cta_o[8 * 128];
+  __shared__ float cta_m[TF_WARPS], cta_l[TF_WARPS];
+  __shared__ __align__(16) float cta_o[TF_WARPS * 128];
   __shared__ __align__(16) float recv[TF_CLUSTER][20];   // per source rank: 16 dims, max, sum
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr int cs = TF_CLUSTER;
@@ -116,8 +117,8 @@ attn_tree_fused_kernel(const TreeFusedArgs a) {
   const int rep = a.H / a.Hkv, hk = hq / rep;
   const int grp = tid >> 3, sub = tid & 7;
   const unsigned gmask = 0xffu << (lane & 24);
-  constexpr int ngroups = 32 * cs;
-  const int gidx = rank * 32 + grp;
+  constexpr int ngroups = (TF_THREADS / 8) * cs;
+  const int gidx = rank * (TF_THREADS / 8) + grp;
   const float scale_log2 = (1.0f / sqrtf(128.0f)) * 1.4426950408889634f;
   // positions and the prefix length were written before the previous launch started, and cache
   // rows below `pos` by earlier decode steps: none of this waits for the previous launch
@@ -293,11 +294,11 @@ attn_tree_fused_kernel(const TreeFusedArgs a) {
   if (tid < 128) {
     float Mx = -CUDART_INF_F;
 #pragma unroll
-    for (int q = 0; q < 8; ++q) Mx = fmaxf(Mx, cta_m[q]);
+    for (int q = 0; q < TF_WARPS; ++q) Mx = fmaxf(Mx, cta_m[q]);
     float Ls = 0.f, acc = 0.f;
     if (Mx > -CUDART_INF_F) {
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
+      for (int q = 0; q < TF_WARPS; ++q) {
         const float w = exp2f(cta_m[q] - Mx);
         Ls = fmaf(cta_l[q], w, Ls);
         acc = fmaf(cta_o[q * 128 + tid], w, acc);

@@ -448,7 +448,7 @@ def test_rope_kv_append_and_tree_decode(K):
 def test_attn_tree_fused_matches_two_call_path(K, plen, maxP, use_pdl):
     """The single-launch small-width attention (rotary + append + attention per cluster) against
     q40_rope_kv_append + q40_attn_tree_decode: identical cache bytes, outputs within fp32 merge
-    order.  1100 prompt keys exceed what the cluster holds in registers at once (768), so that
+    order.  1100 prompt keys exceed what the cluster holds in registers at once (640), so that
     case also runs the second batch of keys; an empty prompt leaves some key groups idle."""
     from spec_mcts_b200._lib import check, lib
     rng = np.random.default_rng(12)
