@@ -108,7 +108,7 @@ attn_tree_fused_kernel(const TreeFusedArgs a) {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   __shared__ float cta_m[TF_WARPS], cta_l[TF_WARPS];
   __shared__ __align__(16) float cta_o[TF_WARPS * 128];
-  __shared__ __align__(16) float recv[TF_CLUSTER][20];   // per source rank: 16 dims, max, sum
+  __shared__ __align__(16) float recv[TF_CLUSTER][128 / TF_CLUSTER + 4];   // per source rank: this rank's dims, max, sum
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr int cs = TF_CLUSTER;
   const int rank = (int)cluster.block_rank();
@@ -307,7 +307,7 @@ attn_tree_fused_kernel(const TreeFusedArgs a) {
     // hand the CTA's partial to the rank that finishes this dim
     float* dst = cluster.map_shared_rank(&recv[rank][0], tid / per);
     dst[tid % per] = acc;
-    if (tid % per == 0) { dst[16] = Mx; dst[17] = Ls; }
+    if (tid % per == 0) { dst[per] = Mx; dst[per + 1] = Ls; }
   }
   Q40_STAMP(5);
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -316,13 +316,13 @@ attn_tree_fused_kernel(const TreeFusedArgs a) {
   if (tid < per) {
     float Mx = -CUDART_INF_F;
 #pragma unroll
-    for (int r = 0; r < cs; ++r) Mx = fmaxf(Mx, recv[r][16]);
+    for (int r = 0; r < cs; ++r) Mx = fmaxf(Mx, recv[r][per]);
     float Ls = 0.f, acc = 0.f;
 #pragma unroll
     for (int r = 0; r < cs; ++r) {
-      const float pm = recv[r][16];
+      const float pm = recv[r][per];
       const float w = (pm > -CUDART_INF_F) ? exp2f(pm - Mx) : 0.f;
-      Ls = fmaf(recv[r][17], w, Ls);
+      Ls = fmaf(recv[r][per + 1], w, Ls);
       acc = fmaf(recv[r][tid], w, acc);
     }
     a.ao[(int64_t)b * (a.H * 128) + hq * 128 + rank * per + tid] = __float2half_rn(Ls > 0.f ? acc / Ls : 0.f);

@@ -220,6 +220,9 @@ class Transformer(nn.Module):
         # shared prompt once for all branches with the three-launch path
         self.use_fused_attn = True
         self.fused_attn_max_width = 1
+        # ... and while prompt + suffix fit in two register batches of its clusters (640 keys each);
+        # longer contexts go through the tensor-core prefix pass
+        self.fused_attn_max_keys = 1280
         self._layer_table = None
         self._lm_head_q4 = None     # set by quantize_lm_head()
         self._trace = None       # optional int64 tensor [6 * n_layers + 8]: barrier timestamps of the step kernel
@@ -381,6 +384,11 @@ class Transformer(nn.Module):
                                  ss_out.data_ptr() if ss_out is not None else None, ss_out_count,
                                  self.max_cluster, 1 if self.use_pdl else 0, st), "q40_gemv_fused")
 
+    def _fused_attn_for(self, B):
+        p = self.params
+        return (self.use_fused_attn and B <= self.fused_attn_max_width and
+                p.max_prompt_seq_len + p.max_seq_len <= self.fused_attn_max_keys)
+
     def _decode_body_fused(self, B):
         """Decode step for B <= 16 branches: 7 launches per layer (qkv with RMSNorm prologue,
         rope+append, 2 attention, wo with residual epilogue, w1/w3 with RMSNorm prologue and
@@ -403,7 +411,7 @@ class Transformer(nn.Module):
             att, ff = layer.attention, layer.feed_forward
             self._fused(1, [att.wq, att.wk, att.wv], [q, k, v], W, h, p.dim, B,
                         norm_w=layer.attention_norm.weight, ss_in=ss_ffn, ss_in_count=c_ffn, st=st)
-            if self.use_fused_attn and B <= self.fused_attn_max_width:
+            if self._fused_attn_for(B):
                 pk, pv = att.cache_prompt_k, att.cache_prompt_v
                 check(lib.q40_attn_tree_fused(qkv.data_ptr(), W, pk.data_ptr(), pv.data_ptr(), att.cache_k.data_ptr(),
                                               att.cache_k_s.data_ptr(), att.cache_v.data_ptr(),
@@ -587,7 +595,7 @@ class Transformer(nn.Module):
         buffers (`_tok_dev`, `_pos_dev`); returns the static logits buffer [B, vocab]."""
         fused = self.use_fused and B <= 16 and self.tp_world == 1
         mega = self.use_megakernel and B <= 8 and self.tp_world == 1
-        self.launches_per_step = 1 if mega else self.params.n_layers * ((5 if self.use_fused_attn and B <= self.fused_attn_max_width else 7) if fused else 13) + (2 if fused else 1)
+        self.launches_per_step = 1 if mega else self.params.n_layers * ((5 if self._fused_attn_for(B) else 7) if fused else 13) + (2 if fused else 1)
         if not self.use_cuda_graph:
             return self._decode_body(B)
         key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster, self.use_megakernel,
