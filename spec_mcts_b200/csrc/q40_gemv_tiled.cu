@@ -58,7 +58,9 @@ struct TiledParams {
   const __half* a;     // [M, lda] activations; with PRO_NORM the un-normalised residual stream
   int64_t lda, ldc;
   int M, K, rows_per_split;
-  // PRO_NORM: x = fp16(fp16(a * rsqrt(sum(ss_in[m][:]) / K + eps)) * norm_w)
+  // PRO_NORM: the activations are fp16(a * norm_w) and every finished sum is multiplied by
+  // rsqrt(sum(ss_in[m][:]) / K + eps) in fp32 (the reference rounds fp16(fp16(a * rsqrt(..)) * norm_w)
+  // before the matmul; the difference is one fp16 rounding of the operand, like the scale placement)
   const __half* norm_w;
   const float* ss_in;
   int ss_in_count;
@@ -134,11 +136,13 @@ gemv_tiled_kernel(const TiledParams p) {
   const int nsteps = (ke > kb) ? (ke - kb + 15) / 16 : 0;
   const int xs_ld = p.rows_per_split + F_XS_PAD;
 
-  // shared memory: [ring: FW x DEPTH slots][xs: MT*8 rows][s_inv: 16 floats]; after the main loop the
-  // ring is reused for the warp slabs and the CTA partial
+  // shared memory: [ring: FW x DEPTH slots][xs: MT*8 rows] ... [s_inv: 16 floats][recv]; after the main
+  // loop the front is reused for the warp slabs
   unsigned char* ring = smem;
   __half* xs = reinterpret_cast<__half*>(smem + FW * F_DEPTH * F_SLOT_BYTES);
-  float* s_inv = reinterpret_cast<float*>(smem + FW * F_DEPTH * F_SLOT_BYTES + MT * 8 * xs_ld * 2);
+  // 1/rms per row (RMSNorm prologue): 16 floats right below the receive buffer, clear of everything the
+  // reduction reuses
+  float* s_inv = reinterpret_cast<float*>(smem + p.recv_off - 64);
   const uint32_t ring_u32 = (uint32_t)__cvta_generic_to_shared(ring) + warp * (F_DEPTH * F_SLOT_BYTES);
   // [recv: nranks x M x slice floats] partial sums pushed by the cluster; a region of its own, because
   // neighbours may push while this CTA is still in its main loop
@@ -180,23 +184,27 @@ gemv_tiled_kernel(const TiledParams p) {
 
   // ---- activations of this k range: raw copy first (and the norm weights), so that the loads do
   // not wait for the row statistics; then, for the RMSNorm prologue, normalise in place ----
-  __half* wn = reinterpret_cast<__half*>(s_inv + 16);     // [rows_per_split] norm weights of this range
   {
     const int chunks = p.rows_per_split / 8;
     for (int idx = tid; idx < MT * 8 * chunks; idx += FT) {
       const int m = idx / chunks, kk = (idx % chunks) * 8;
       uint4 v = make_uint4(0, 0, 0, 0);
       const int k = kb + kk;
-      if (m < p.M && k < ke) v = *reinterpret_cast<const uint4*>(p.a + (int64_t)m * p.lda + k);
+      if (m < p.M && k < ke) {
+        v = *reinterpret_cast<const uint4*>(p.a + (int64_t)m * p.lda + k);
+        if (PRO == PRO_NORM) {
+          // RMSNorm prologue: the norm weight is applied here, the row's 1/rms (a scalar per row) to
+          // the finished sums in the epilogue, so that nothing at the start of the launch waits for it
+          const uint4 wv = *reinterpret_cast<const uint4*>(p.norm_w + k);
+          __half2* vh = reinterpret_cast<__half2*>(&v);
+          const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) vh[j] = __hmul2(vh[j], wh[j]);
+        }
+      }
       *reinterpret_cast<uint4*>(xs + m * xs_ld + kk) = v;
     }
     if (PRO == PRO_NORM) {
-      for (int idx = tid; idx < chunks; idx += FT) {
-        const int k = kb + idx * 8;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (k < ke) v = *reinterpret_cast<const uint4*>(p.norm_w + k);
-        *reinterpret_cast<uint4*>(wn + idx * 8) = v;
-      }
       for (int m = warp; m < p.M; m += FW) {
         // all loads in flight before the first add (the partials sit in L2)
         float s = 0.f;
@@ -217,24 +225,6 @@ gemv_tiled_kernel(const TiledParams p) {
     }
   }
   __syncthreads();
-  if (PRO == PRO_NORM) {
-    const int chunks = p.rows_per_split / 8;
-    for (int idx = tid; idx < p.M * chunks; idx += FT) {
-      const int m = idx / chunks, kk = (idx % chunks) * 8;
-      uint4 v = *reinterpret_cast<const uint4*>(xs + m * xs_ld + kk);
-      const uint4 wv = *reinterpret_cast<const uint4*>(wn + kk);
-      __half2* vh = reinterpret_cast<__half2*>(&v);
-      const __half2* wh = reinterpret_cast<const __half2*>(&wv);
-      const float inv = s_inv[m];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __half22float2(vh[j]);
-        vh[j] = __hmul2(__floats2half2_rn(f.x * inv, f.y * inv), wh[j]);
-      }
-      *reinterpret_cast<uint4*>(xs + m * xs_ld + kk) = v;
-    }
-    __syncthreads();
-  }
 
   Q40_STAMP(3);
   float acc[MT][NT][4];
@@ -343,6 +333,7 @@ gemv_tiled_kernel(const TiledParams p) {
   const int npart = (EPI == EPI_SILU) ? nranks / 2 : nranks;
   for (int m = warp; m < p.M; m += FW) {
     float ssq = 0.f;
+    const float inv = (PRO == PRO_NORM) ? s_inv[m] : 1.0f;
     for (int cidx = lane; cidx < slice; cidx += 32) {
       const int lc = rank * slice + cidx;
       const float* rp = recv + m * slice + cidx;
@@ -356,6 +347,7 @@ gemv_tiled_kernel(const TiledParams p) {
       } else {
         for (int r = 0; r < npart; ++r) v0 += rp[r * rstride];
       }
+      if (PRO == PRO_NORM) { v0 *= inv; v1 *= inv; }
       const int n = f_span_col(span, lc);
       if (n < pr.N) {
         if (EPI == EPI_STORE) {
@@ -387,10 +379,10 @@ static int launch_tiled(const TiledParams& p, int grid_x, int nsplit, int cluste
   auto kern = gemv_tiled_kernel<MT, NG, KS, PRO, EPI>;
   constexpr int FW = (4 / NG) * KS, FT = FW * 32, NT = NG * 4;
   const size_t ring = (size_t)FW * F_DEPTH * NG * F_GROUP_BYTES;
-  const size_t xs = (size_t)MT * 8 * (p.rows_per_split + F_XS_PAD) * 2 + 64 + (size_t)p.rows_per_split * 2;
+  const size_t xs = (size_t)MT * 8 * (p.rows_per_split + F_XS_PAD) * 2;
   const size_t red = (size_t)FW * MT * NT * 32 * 16;
   size_t smem = (ring + xs) > red ? (ring + xs) : red;
-  smem = (smem + 15) / 16 * 16;
+  smem = (smem + 15) / 16 * 16 + 64;            // + the table of 1/rms per row
   TiledParams pp = p;
   pp.recv_off = (int)smem;
   smem += (size_t)p.M * F_SPAN_COLS * 4;        // receive buffer of the cluster reduction

@@ -22,7 +22,12 @@ def dev(a):
 
 
 def close(a, b, rtol=2e-2, atol=1e-2):
-    np.testing.assert_allclose(a.astype(np.float32), b.astype(np.float32), rtol=rtol, atol=atol)
+    """rel 2e-2 / abs 1e-2, the absolute floor raised to 2e-3 of the output's mean magnitude where that is
+    larger (outputs of scale 8 have an fp16 ulp of 0.0078: an element that happens to land near zero
+    cannot be held to 1e-2 when the rounding point of one operand differs)."""
+    bf = b.astype(np.float32)
+    atol = max(atol, 2e-3 * float(np.abs(bf).mean()))
+    np.testing.assert_allclose(a.astype(np.float32), bf, rtol=rtol, atol=atol)
 
 
 def qmat(rng, K_, N, std):
@@ -116,9 +121,16 @@ def test_layer_chain_modes_1_2_3(K, M, dims, tiled):
     # mode 3 from the GPU's h2 / ss2
     g = K.gemv_fused(3, h2, [D(w1, (dim, hid)), D(w3, (dim, hid))], norm_w=dev(nw), ss_in=ss2, use_pdl=True, tiled=tiled)
     xn2 = O.rmsnorm(h2_np, nw, 1e-5)
-    gref = O.silu_mul(O.matmul_q40(xn2, *w1, (dim, hid)), O.matmul_q40(xn2, *w3, (dim, hid)))
-    # a product of two matmul outputs: their tolerances add
-    close(g.cpu().numpy(), gref, rtol=3e-2, atol=8e-2)
+    a1ref, a3ref = O.matmul_q40(xn2, *w1, (dim, hid)), O.matmul_q40(xn2, *w3, (dim, hid))
+    gref = O.silu_mul(a1ref, a3ref)
+    # g = silu(a1) * a3 with each factor inside the matmul tolerance (rel 2e-2 / abs 1e-2): the error of the
+    # product is bounded by |a3| * d(silu(a1)) + |silu(a1)| * d(a3), with |d silu| <= 1.1 |d a1|
+    a1f, a3f = a1ref.astype(np.float32), a3ref.astype(np.float32)
+    sil = a1f / (1.0 + np.exp(-a1f))
+    tol = (np.abs(a3f) * 1.1 * (2e-2 * np.abs(a1f) + 1e-2) + np.abs(sil) * (2e-2 * np.abs(a3f) + 1e-2)
+           + 2e-2 * np.abs(gref.astype(np.float32)) + 1e-2)
+    err = np.abs(g.cpu().numpy().astype(np.float32) - gref.astype(np.float32))
+    assert (err <= tol).all(), float((err - tol).max())
     # mode 2 again (w2), in place
     g_np = g.cpu().numpy()
     h3, ss3 = K.gemv_fused(2, g, [D(w2, (hid, dim))], h_in=h2, use_pdl=True, tiled=tiled)
