@@ -167,27 +167,26 @@ int q40_gemv_tiled(int mode, int nmat, const void* const* bw, const void* const*
                    void* stream);
 int q40_gemv_tiled_ss_count(int N, int K, int max_cluster);
 
-/* One whole decode step of the KV-shared Q4_0 model for 1 <= M <= 8 branches as a single
- * persistent launch: embedding, every layer ([wq,wk,wv] with RMSNorm, rotary embedding + Q4_0
- * cache append + attention over shared prompt / packed suffix / new token, wo + residual,
- * [w1,w3] with RMSNorm and SiLU-mul, w2 + residual) and the final RMSNorm, which is left in `xn`
- * [M, dim] for the caller's lm_head.  `layers` is a device array of n_layers records of 22
- * device pointers: packed weights wq wk wv wo w1 w3 w2, their scales in the same order,
- * attention_norm, ffn_norm, prompt K, prompt V ([max_p, Hkv, 128] fp16), suffix K bytes, K scales,
- * V bytes, V scales ([maxB, max_t, Hkv, 64] / [.., 2]).  tokens int64 [M], pos int32 [M] (absolute
- * positions), prefix_len int32 [1], cos/sin fp16 [n_pos, 64].  h/qkv/ao/g/xn, ss_a/ss_f
- * ([M, 1024] floats), bar and err are caller-owned device scratch; bar and err are zeroed on the
- * stream by this call; *err != 0 afterwards means a bounded wait between CTAs expired and the
- * result is undefined.  max_cluster 16 or 8.  `trace` is NULL or a device array of
- * 6 * n_layers + 8 words that receives the GPU timer after every grid-wide barrier (profiling aid).  Needs an otherwise idle GPU (all CTAs must be
- * resident at once).
- * Replaces: Transformer.forward for one decode step (hf_model_q40_kv_shared.py:492-510). */
-int q40_decode_step(const void* layers, int n_layers, int M, int dim, int H, int Hkv, int hidden,
-                    int vocab, int max_t, int max_p, int n_pos, float eps, const void* emb,
-                    const void* final_norm, const int64_t* tokens, const int32_t* pos,
-                    const int32_t* prefix_len, const void* cos_tbl, const void* sin_tbl, void* h,
-                    void* qkv, void* ao, void* g, void* xn, float* ss_a, float* ss_f,
-                    unsigned int* bar, int* err, int max_cluster, unsigned long long* trace, void* stream);
+/* The decode matmul as one byte-balanced wave (stream-K): the same modes and results as
+ * q40_gemv_tiled on the same tiled copies, except that modes 1 and 3 keep the reference's RMSNorm
+ * rounding points (fp16(fp16(float(a) / rms) * norm_w) is the operand).  One CTA per SM at most, each
+ * streaming an equal contiguous share of the launch's weight bytes through a shared-memory ring filled
+ * by 1-D bulk copies; the partial sums of a 256-column span meet in `workspace` and the CTA that
+ * arrives last adds them in a fixed order, so results are reproducible run to run.
+ * workspace: q40_gemv_stream_workspace_bytes(M, sum of n_cols, K) bytes, 16-byte aligned, zero-filled
+ * once by the caller (the kernels leave its counters zeroed); launches that share it must be ordered on
+ * one stream.  Its first int is a status word: non-zero after a launch means a bounded wait inside the
+ * kernel expired and the outputs of that launch are undefined.  ss_out_count must be
+ * q40_gemv_stream_ss_count(N) = N / 256.  smem_budget: shared memory per CTA in bytes (0 = 100 KiB up to
+ * 4 rows, which lets the CTAs of two consecutive launches share an SM, 200 KiB above).  1 <= M <= 16, every N % 256 == 0.
+ * Replaces: the same reference lines as q40_gemv_fused. */
+size_t q40_gemv_stream_workspace_bytes(int M, int total_cols, int K);
+int q40_gemv_stream(int mode, int nmat, const void* const* bw_tiled, void* const* out, const int* n_cols,
+                    int64_t ldc, const void* a, int64_t lda, int M, int K, const void* norm_w,
+                    const float* ss_in, int ss_in_count, float eps, const void* h_in, int64_t ldh,
+                    float* ss_out, int ss_out_count, void* workspace, size_t workspace_bytes,
+                    int smem_budget, int use_pdl, void* stream);
+int q40_gemv_stream_ss_count(int N);
 
 /* ---- decode attention (one query token per branch) ---------------------------------- */
 

@@ -87,10 +87,10 @@ class ModelOracle:
         return (hn.astype(F32) @ self.out.astype(F32).T).astype(F16)
 
 
-def from_golden(g):
+def from_golden(g, max_batch_size=4):
     """Build the oracle from the arrays of tests/golden/model_small.npz."""
     hidden = int(g["hidden"])
-    m = ModelOracle(256, 2, 2, 2, 512, hidden, 1e-5, 1e6, 4, 16, 32)
+    m = ModelOracle(256, 2, 2, 2, 512, hidden, 1e-5, 1e6, max_batch_size, 16, 32)
     m.emb = g["sd.tok_embeddings.weight"]
     m.out = g["sd.output.weight"]
     m.norm["norm"] = g["sd.norm.weight"]

@@ -61,10 +61,11 @@ SIGNATURES = {
     "q40_gemv_tiled_ss_count": (c_int, [c_int, c_int, c_int]),
     "q40_tiled_bytes": (c_size_t, [c_int, c_int]),
     "q40_relayout_tiled": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
-    "q40_decode_step": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                c_void_p, c_int, c_void_p, c_void_p]),
+    "q40_gemv_stream_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "q40_gemv_stream": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int,
+                                c_void_p, c_void_p, c_int, c_float, c_void_p, c_int64, c_void_p, c_int, c_void_p,
+                                c_size_t, c_int, c_int, c_void_p]),
+    "q40_gemv_stream_ss_count": (c_int, [c_int]),
     "q40_attn_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p]),
     "q40_attn_paged": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -22,7 +22,7 @@ __all__ = [
     "quantize_q40", "dequantize_q40", "triton_deq_int40", "triton_q_int40", "triton_q_int40_sliced",
     "quantize_q40_rows", "matmul", "matmul_q40", "linear_q40", "flash_attn", "page_flash_attn",
     "triton_attn", "chunk_attn", "shared_prefix_attn", "matmul_split_k", "rmsnorm", "rope_", "silu_mul",
-    "gemv_fused", "embed_rows", "tc_error_flag", "relayout_tiled",
+    "gemv_fused", "gemv_stream", "stream_status", "embed_rows", "tc_error_flag", "relayout_tiled", "relayout_cache_config",
     "Q40Error",
 ]
 
@@ -151,10 +151,16 @@ def triton_q_int40_sliced(w: torch.Tensor, b_end, q_start, q_end):
 # matmuls
 # --------------------------------------------------------------------------------------
 def matmul_q40(a: torch.Tensor, b_w: torch.Tensor, b_s: torch.Tensor, b_shape, *,
-               group_size: int = GROUP_SIZE, out: Optional[torch.Tensor] = None):
+               group_size: int = GROUP_SIZE, out: Optional[torch.Tensor] = None, relayout: Optional[bool] = None):
     """C = A @ deq(B); same call as the reference's matmul_q40 (triton_kernels.py:471-500):
     a [M,K] fp16 contiguous, b_w/b_s the packed weight and scales of a [K,N] matrix
-    quantised row-major (groups along N), b_shape = (K, N).  Returns fp16 [M,N]."""
+    quantised row-major (groups along N), b_shape = (K, N).  Returns fp16 [M,N].
+
+    Up to 16 rows with N % 256 == 0 the weight is read through a tiled copy that is made the first time
+    a given (b_w, b_s) pair of tensors is seen and kept while those tensor objects live and are not
+    written in place (the reference's LinearQ4_0 passes the same `.w` / `.s` attributes on every call,
+    hf_model_q40_kv_shared.py:228-236).  The copy doubles the device memory of that weight;
+    `relayout=False` (or relayout_cache_config(enabled=False)) reads the checkpoint layout instead."""
     dev = _need_cuda(a, b_w, b_s)
     assert a.is_contiguous(), "Matrix A must be contiguous"
     M, K = a.shape
@@ -169,8 +175,12 @@ def matmul_q40(a: torch.Tensor, b_w: torch.Tensor, b_s: torch.Tensor, b_shape, *
     c = out if out is not None else torch.empty((M, N), device=dev, dtype=torch.float16)
     if M == 0:
         return c
-    if (M <= 16 and group_size == 64 and N % 128 == 0 and K % 16 == 0 and K >= 64 and a.data_ptr() % 16 == 0
-            and c.stride(1) == 1 and _cluster_gemv(dev, a, b_w, b_s, c, M, N, K)):
+    small = M <= 16 and group_size == 64 and K % 16 == 0 and K >= 64 and a.data_ptr() % 16 == 0 and c.stride(1) == 1
+    if small and N % 256 == 0 and (relayout if relayout is not None else _relayout_cfg["enabled"]):
+        tiled = _tiled_copy_of(b_w, b_s, K, N)
+        if tiled is not None and (_tiled_gemv(dev, a, tiled, c, M, N, K) or _stream_gemv(dev, a, tiled, c, M, N, K)):
+            return c
+    if small and N % 128 == 0 and _cluster_gemv(dev, a, b_w, b_s, c, M, N, K):
         return c
     nbytes = lib.q40_gemm_workspace_bytes(M, N, K)
     ws = _workspace("gemm", dev, nbytes, zero=True)
@@ -181,6 +191,96 @@ def matmul_q40(a: torch.Tensor, b_w: torch.Tensor, b_s: torch.Tensor, b_shape, *
 
 
 _cluster_size = {}      # device index -> largest cluster the device schedules for the decode matmul (16 or 8)
+
+# tiled copies made for matmul_q40: id(b_w) -> (weakref to b_w, weakref to b_s, versions, (K, N), copy)
+_relayout_cfg = {"enabled": True, "max_bytes": 48 << 30}
+_relayout_cache: dict = {}
+_relayout_bytes = [0]
+
+
+def relayout_cache_config(enabled: Optional[bool] = None, max_bytes: Optional[int] = None, clear: bool = False):
+    """Control the tiled copies matmul_q40 keeps per weight tensor: switch them off, cap their total
+    size (beyond the cap new weights are read in the checkpoint layout), or drop them all."""
+    if enabled is not None:
+        _relayout_cfg["enabled"] = bool(enabled)
+    if max_bytes is not None:
+        _relayout_cfg["max_bytes"] = int(max_bytes)
+    if clear:
+        _relayout_cache.clear()
+        _relayout_bytes[0] = 0
+    return dict(_relayout_cfg, bytes_in_use=_relayout_bytes[0], entries=len(_relayout_cache))
+
+
+def _versions(*ts):
+    """In-place modification counters (tensors made under inference_mode keep none and cannot be
+    written in place outside it)."""
+    out = []
+    for t in ts:
+        try:
+            out.append(t._version)
+        except RuntimeError:
+            out.append(-1)
+    return tuple(out)
+
+
+def _tiled_copy_of(b_w, b_s, K, N):
+    import weakref
+    key = id(b_w)
+    ent = _relayout_cache.get(key)
+    if ent is not None:
+        rw, rs, ver, shape, ptrs, copy = ent
+        if (rw() is b_w and rs() is b_s and ver == _versions(b_w, b_s) and shape == (K, N)
+                and ptrs == (b_w.data_ptr(), b_s.data_ptr())):
+            return copy
+        _relayout_bytes[0] -= copy.numel()
+        del _relayout_cache[key]
+    nbytes = lib.q40_tiled_bytes(N, K)
+    if nbytes == 0 or _relayout_bytes[0] + nbytes > _relayout_cfg["max_bytes"]:
+        return None
+    copy = relayout_tiled(b_w, b_s, (K, N))
+
+    def _drop(_ref, key=key):
+        e = _relayout_cache.pop(key, None)
+        if e is not None:
+            _relayout_bytes[0] -= e[5].numel()
+
+    _relayout_cache[key] = (weakref.ref(b_w, _drop), weakref.ref(b_s), _versions(b_w, b_s), (K, N),
+                            (b_w.data_ptr(), b_s.data_ptr()), copy)
+    _relayout_bytes[0] += nbytes
+    return copy
+
+
+def _tiled_gemv(dev, a, tiled, c, M, N, K) -> bool:
+    """Mode 0 of q40_gemv_tiled (cluster split-K) on a tiled copy; False if this device cannot schedule
+    the clusters."""
+    import ctypes
+    P = ctypes.c_void_p * 1
+    for cluster in ((_cluster_size.get(dev.index, 16),) if dev.index in _cluster_size else (16, 8)):
+        rc = lib.q40_gemv_tiled(0, 1, P(tiled.data_ptr()), P(0), P(c.data_ptr()), (ctypes.c_int * 1)(N), c.stride(0),
+                                a.data_ptr(), a.stride(0), M, K, None, None, 0, 0.0, None, 0, None, 0, cluster, 0,
+                                _stream(dev))
+        if rc == 0:
+            _cluster_size[dev.index] = cluster
+            return True
+        if rc > 0:
+            check(rc, "q40_gemv_tiled")
+    return False
+
+
+def _stream_gemv(dev, a, tiled, c, M, N, K) -> bool:
+    """Mode 0 of q40_gemv_stream on a tiled copy; False if the launch was refused for this shape."""
+    import ctypes
+    P = ctypes.c_void_p * 1
+    nbytes = lib.q40_gemv_stream_workspace_bytes(M, N, K)
+    if nbytes == 0:
+        return False
+    ws = _workspace("stream", dev, nbytes, zero=True)
+    rc = lib.q40_gemv_stream(0, 1, P(tiled.data_ptr()), P(c.data_ptr()), (ctypes.c_int * 1)(N), c.stride(0),
+                             a.data_ptr(), a.stride(0), M, K, None, None, 0, 0.0, None, 0, None, 0, ws.data_ptr(),
+                             ws.numel(), 0, 0, _stream(dev))
+    if rc > 0:
+        check(rc, "q40_gemv_stream")
+    return rc == 0
 
 
 def _cluster_gemv(dev, a, b_w, b_s, c, M, N, K) -> bool:
@@ -289,6 +389,59 @@ def gemv_fused(mode: int, a: torch.Tensor, weights, *, norm_w=None, ss_in=None, 
     if mode == 3:
         return outs[0]
     return outs
+
+
+def gemv_stream(mode: int, a: torch.Tensor, weights, *, norm_w=None, ss_in=None, eps: float = 1e-5, h_in=None,
+                use_pdl: bool = False, smem_budget: int = 0, workspace: Optional[torch.Tensor] = None):
+    """gemv_fused on the byte-balanced stream-K launch (q40_gemv_stream in include/q40b200.h).
+    `weights` is a list of 1-3 (tiled copy, (K, N)) pairs sharing the activations a [M <= 16, K];
+    same modes and return values as gemv_fused.  Also returns nothing else: the kernel's status word
+    is the first int of `workspace` (a zero-filled uint8 tensor of q40_gemv_stream_workspace_bytes)."""
+    import ctypes
+    dev = _need_cuda(a, norm_w, ss_in, h_in, *[w[0] for w in weights])
+    M, K = a.shape
+    n = len(weights)
+    Ns = [int(w[1][1]) for w in weights]
+    for w in weights:
+        assert int(w[1][0]) == K
+    P = ctypes.c_void_p * n
+    if mode == 3:
+        outs = [torch.empty((M, Ns[0]), dtype=torch.float16, device=dev)] * 2
+        ldc = Ns[0]
+    else:
+        buf = torch.empty((M, sum(Ns)), dtype=torch.float16, device=dev)
+        outs, c0 = [], 0
+        for N in Ns:
+            outs.append(buf[:, c0:c0 + N])
+            c0 += N
+        ldc = sum(Ns)
+    ss_out, cnt = None, 0
+    if mode == 2:
+        cnt = lib.q40_gemv_stream_ss_count(Ns[0])
+        ss_out = torch.empty((M, cnt), dtype=torch.float32, device=dev)
+    nbytes = lib.q40_gemv_stream_workspace_bytes(M, sum(Ns), K)
+    if nbytes == 0:
+        raise Q40Error(f"gemv_stream: unsupported shape M={M} N={Ns} K={K}")
+    ws = workspace if workspace is not None else _workspace("stream", dev, nbytes, zero=True)
+    a = a.contiguous()
+    check(lib.q40_gemv_stream(mode, n, P(*[w[0].data_ptr() for w in weights]), P(*[o.data_ptr() for o in outs]),
+                              (ctypes.c_int * n)(*Ns), ldc, a.data_ptr(), a.stride(0), M, K, _ptr(norm_w),
+                              _ptr(ss_in), ss_in.shape[1] if ss_in is not None else 0, float(eps), _ptr(h_in),
+                              h_in.stride(0) if h_in is not None else 0, _ptr(ss_out), cnt, ws.data_ptr(),
+                              ws.numel(), smem_budget, 1 if use_pdl else 0, _stream(dev)), "q40_gemv_stream")
+    if mode == 2:
+        return outs[0], ss_out
+    if mode == 3:
+        return outs[0]
+    return outs
+
+
+def stream_status(dev=None) -> int:
+    """Status word of the stream-K launches made through this module on the current stream of `dev`
+    (non-zero: a bounded wait inside a kernel expired; synchronises the device)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if dev is None else dev
+    buf = _workspaces.get(("stream", dev.index, _stream(dev)))
+    return 0 if buf is None else int(buf[:4].view(torch.int32).item())
 
 
 def embed_rows(emb: torch.Tensor, tokens: torch.Tensor, ss_count: int):

@@ -211,10 +211,12 @@ class Transformer(nn.Module):
         self.use_fused = True
         self.use_pdl = True
         self.max_cluster = 16
-        # B <= 8 without tensor parallelism can run the whole step as one persistent kernel
-        self.use_megakernel = False
         # B <= 16: the fused matmuls read a rearranged ("tiled") copy of each weight, made on first use
         self.use_tiled = True
+        # ... True: through the byte-balanced stream-K launch (one CTA per SM, bulk-copy ring, no clusters);
+        # False: the cluster-reduced launch on the same tiled copies (faster on B200, the default)
+        self.use_stream = False
+        self.stream_smem_budget = 0      # 0 = the library's default (two launches' CTAs share an SM)
         # width <= 16: rotary embedding, cache append and attention as one cluster launch
         # single-launch attention (rotary + append + attention) up to this width; wider steps read the
         # shared prompt once for all branches with the three-launch path
@@ -223,9 +225,7 @@ class Transformer(nn.Module):
         # ... and while prompt + suffix fit in two register batches of its clusters (640 keys each);
         # longer contexts go through the tensor-core prefix pass
         self.fused_attn_max_keys = 1280
-        self._layer_table = None
         self._lm_head_q4 = None     # set by quantize_lm_head()
-        self._trace = None       # optional int64 tensor [6 * n_layers + 8]: barrier timestamps of the step kernel
 
     # ------------------------------------------------------------------ reference API
     @torch.inference_mode()
@@ -306,7 +306,6 @@ class Transformer(nn.Module):
                      attn_ws=torch.empty(nb_attn, dtype=torch.uint8, device=dev),
                      gemm_ws=torch.zeros(nb_gemm, dtype=torch.uint8, device=dev),
                      logits=e(B, p.vocab_size), qkv=e(B, (H + 2 * Hkv) * D),
-                     sync=torch.zeros(2, dtype=torch.int32, device=dev),
                      ss_attn=torch.zeros((B, 1024), dtype=torch.float32, device=dev),
                      ss_ffn=torch.zeros((B, 1024), dtype=torch.float32, device=dev))
             self._bufs[B] = b
@@ -342,8 +341,6 @@ class Transformer(nn.Module):
 
     def _decode_body(self, B):
         """Enqueue one decode step for B branches on the current stream (captured into a graph)."""
-        if self.use_megakernel and B <= 8 and self.tp_world == 1:
-            return self._decode_body_mega(B)
         if self.use_fused and B <= 16 and self.tp_world == 1:
             return self._decode_body_fused(B)
         return self._decode_body_unfused(B)
@@ -362,8 +359,29 @@ class Transformer(nn.Module):
             out.append(l._tiled)
         return out
 
+    def _streamable(self, lins, M):
+        return self.use_tiled and self.use_stream and M <= 16 and all(self._tileable(l) for l in lins)
+
+    def _stream_ws(self, bufs, M):
+        """Workspace of the stream-K launches of one step (they run one after the other on one stream)."""
+        ws = bufs.get("stream_ws")
+        if ws is None:
+            p, hid = self.params, self.layers[0].feed_forward.hidden_dim
+            H, Hkv, D = self._H, self._Hkv, self._D
+            vp = (p.vocab_size + 255) // 256 * 256
+            shapes = [((H + 2 * Hkv) * D, p.dim), (p.dim, H * D), (2 * hid, p.dim), (p.dim, hid), (vp, p.dim)]
+            nb = max(lib.q40_gemv_stream_workspace_bytes(M, n, k) for n, k in shapes if n % 256 == 0 and k % 16 == 0)
+            ws = bufs["stream_ws"] = torch.zeros(max(nb, 4096), dtype=torch.uint8, device=self.device)
+        return ws
+
+    def _ss_count(self, N, Kd, M, lins):
+        """Sum-of-squares partials per row written by the mode-2 launch that produces N columns."""
+        if self._streamable(lins, M):
+            return lib.q40_gemv_stream_ss_count(N)
+        return lib.q40_gemv_fused_ss_count(N, Kd, self.max_cluster)
+
     def _fused(self, mode, lins, outs, ldc, a, lda, M, norm_w=None, ss_in=None, ss_in_count=0, h_in=None,
-               ldh=0, ss_out=None, ss_out_count=0, st=None):
+               ldh=0, ss_out=None, ss_out_count=0, st=None, bufs=None):
         import ctypes
         n = len(lins)
         P = ctypes.c_void_p * n
@@ -372,17 +390,32 @@ class Transformer(nn.Module):
             bw = P(*[t.data_ptr() for t in self._tiled_of(lins)])
         else:
             bw = P(*[l.w.data_ptr() for l in lins])
-        bs = P(*[l.s.data_ptr() for l in lins])
-        fn = lib.q40_gemv_tiled if tiled else lib.q40_gemv_fused
         op = P(*[o.data_ptr() for o in outs])
         nc = (ctypes.c_int * n)(*[l.kn()[1] for l in lins])
         Kd = lins[0].kn()[0]
-        check(fn(mode, n, bw, bs, op, nc, ldc, a.data_ptr(), lda, M, Kd,
-                                 norm_w.data_ptr() if norm_w is not None else None,
-                                 ss_in.data_ptr() if ss_in is not None else None, ss_in_count,
-                                 float(self.params.norm_eps), h_in.data_ptr() if h_in is not None else None, ldh,
-                                 ss_out.data_ptr() if ss_out is not None else None, ss_out_count,
-                                 self.max_cluster, 1 if self.use_pdl else 0, st), "q40_gemv_fused")
+        nw = norm_w.data_ptr() if norm_w is not None else None
+        si = ss_in.data_ptr() if ss_in is not None else None
+        hi = h_in.data_ptr() if h_in is not None else None
+        so = ss_out.data_ptr() if ss_out is not None else None
+        if tiled and self.use_stream and bufs is not None:
+            ws = self._stream_ws(bufs, M)
+            check(lib.q40_gemv_stream(mode, n, bw, op, nc, ldc, a.data_ptr(), lda, M, Kd, nw, si, ss_in_count,
+                                      float(self.params.norm_eps), hi, ldh, so, ss_out_count, ws.data_ptr(),
+                                      ws.numel(), self.stream_smem_budget, 1 if self.use_pdl else 0, st),
+                  "q40_gemv_stream")
+            return
+        bs = P(*[l.s.data_ptr() for l in lins])
+        fn = lib.q40_gemv_tiled if tiled else lib.q40_gemv_fused
+        check(fn(mode, n, bw, bs, op, nc, ldc, a.data_ptr(), lda, M, Kd, nw, si, ss_in_count,
+                 float(self.params.norm_eps), hi, ldh, so, ss_out_count,
+                 self.max_cluster, 1 if self.use_pdl else 0, st), "q40_gemv_fused")
+
+    def stream_status(self, B) -> int:
+        """Non-zero if a bounded wait inside a stream-K launch of the last steps expired (synchronises)."""
+        b = self._bufs.get(B)
+        if b is None or "stream_ws" not in b:
+            return 0
+        return int(b["stream_ws"][:4].view(torch.int32).item())
 
     def _fused_attn_for(self, B):
         p = self.params
@@ -398,8 +431,9 @@ class Transformer(nn.Module):
         self._check_loaded()
         st = torch.cuda.current_stream(self.device).cuda_stream
         hid = self.layers[0].feed_forward.hidden_dim
-        c_attn = lib.q40_gemv_fused_ss_count(p.dim, H * D, self.max_cluster)    # written by wo
-        c_ffn = lib.q40_gemv_fused_ss_count(p.dim, hid, self.max_cluster)       # written by w2
+        l0 = self.layers[0]
+        c_attn = self._ss_count(p.dim, H * D, B, [l0.attention.wo])             # written by wo
+        c_ffn = self._ss_count(p.dim, hid, B, [l0.feed_forward.w2])             # written by w2
         h, qkv, ao, gbuf = bufs["h"], bufs["qkv"], bufs["ao"], bufs["g"]
         ss_attn, ss_ffn = bufs["ss_attn"], bufs["ss_ffn"]
         W = (H + 2 * Hkv) * D
@@ -410,7 +444,7 @@ class Transformer(nn.Module):
         for layer in self.layers:
             att, ff = layer.attention, layer.feed_forward
             self._fused(1, [att.wq, att.wk, att.wv], [q, k, v], W, h, p.dim, B,
-                        norm_w=layer.attention_norm.weight, ss_in=ss_ffn, ss_in_count=c_ffn, st=st)
+                        norm_w=layer.attention_norm.weight, ss_in=ss_ffn, ss_in_count=c_ffn, st=st, bufs=bufs)
             if self._fused_attn_for(B):
                 pk, pv = att.cache_prompt_k, att.cache_prompt_v
                 check(lib.q40_attn_tree_fused(qkv.data_ptr(), W, pk.data_ptr(), pv.data_ptr(), att.cache_k.data_ptr(),
@@ -434,11 +468,11 @@ class Transformer(nn.Module):
                                                v.data_ptr(), W, ao.data_ptr(), B, H, Hkv, D, aws.data_ptr(),
                                                aws.numel(), st), "q40_attn_tree_decode")
             self._fused(2, [att.wo], [h], p.dim, ao, H * D, B, h_in=h, ldh=p.dim, ss_out=ss_attn,
-                        ss_out_count=c_attn, st=st)
+                        ss_out_count=c_attn, st=st, bufs=bufs)
             self._fused(3, [ff.w1, ff.w3], [gbuf, gbuf], hid, h, p.dim, B, norm_w=layer.ffn_norm.weight,
-                        ss_in=ss_attn, ss_in_count=c_attn, st=st)
+                        ss_in=ss_attn, ss_in_count=c_attn, st=st, bufs=bufs)
             self._fused(2, [ff.w2], [h], p.dim, gbuf, hid, B, h_in=h, ldh=p.dim, ss_out=ss_ffn,
-                        ss_out_count=c_ffn, st=st)
+                        ss_out_count=c_ffn, st=st, bufs=bufs)
         if self._lm_head_q4 is not None:
             # final RMSNorm as the prologue of the Q4_0 lm_head launch; the padded columns are cut off
             lin = self._lm_head_q4
@@ -446,7 +480,7 @@ class Transformer(nn.Module):
             if "logits_pad" not in bufs:
                 bufs["logits_pad"] = torch.empty((B, vp), dtype=DTYPE, device=self.device)
             self._fused(1, [lin], [bufs["logits_pad"]], vp, h, p.dim, B, norm_w=self.norm.weight, ss_in=ss_ffn,
-                        ss_in_count=c_ffn, st=st)
+                        ss_in_count=c_ffn, st=st, bufs=bufs)
             logits = bufs["logits_pad"][:, :p.vocab_size]
         else:
             self._norm(h, None, self.norm.weight, bufs["xn"], st)
@@ -472,48 +506,6 @@ class Transformer(nn.Module):
         lin.shape = (vp, dim)
         self._lm_head_q4 = lin
         self._graphs.clear()
-
-    def _build_layer_table(self):
-        """Device array of per-layer pointer records in the order q40_decode_step documents."""
-        rows = []
-        for layer in self.layers:
-            a, f = layer.attention, layer.feed_forward
-            lins = [a.wq, a.wk, a.wv, a.wo, f.w1, f.w3, f.w2]
-            rows.append([l.w.data_ptr() for l in lins] + [l.s.data_ptr() for l in lins] +
-                        [layer.attention_norm.weight.data_ptr(), layer.ffn_norm.weight.data_ptr(),
-                         a.cache_prompt_k.data_ptr(), a.cache_prompt_v.data_ptr(), a.cache_k.data_ptr(),
-                         a.cache_k_s.data_ptr(), a.cache_v.data_ptr(), a.cache_v_s.data_ptr()])
-        self._layer_table = torch.tensor(rows, dtype=torch.int64).to(self.device)
-
-    def _decode_body_mega(self, B):
-        """Decode step for B <= 8 branches as one persistent kernel plus the fp16 lm_head."""
-        p, bufs = self.params, self._step_buffers(B)
-        self._check_loaded()
-        if self._layer_table is None:
-            self._build_layer_table()
-        st = torch.cuda.current_stream(self.device).cuda_stream
-        hid = self.layers[0].feed_forward.hidden_dim
-        sync = bufs["sync"]
-        check(lib.q40_decode_step(self._layer_table.data_ptr(), p.n_layers, B, p.dim, self._H, self._Hkv, hid,
-                                  p.vocab_size, p.max_seq_len, p.max_prompt_seq_len, self._n_pos,
-                                  float(p.norm_eps), self.tok_embeddings.weight.data_ptr(),
-                                  self.norm.weight.data_ptr(), self._tok_dev.data_ptr(), self._pos_dev.data_ptr(),
-                                  self._prefix_len_dev.data_ptr(), self._cos.data_ptr(), self._sin.data_ptr(),
-                                  bufs["h"].data_ptr(), bufs["qkv"].data_ptr(), bufs["ao"].data_ptr(),
-                                  bufs["g"].data_ptr(), bufs["xn"].data_ptr(), bufs["ss_attn"].data_ptr(),
-                                  bufs["ss_ffn"].data_ptr(), sync.data_ptr(), sync.data_ptr() + 4,
-                                  self.max_cluster, self._trace.data_ptr() if self._trace is not None else None,
-                                  st), "q40_decode_step")
-        torch.matmul(bufs["xn"], self.output.weight.t(), out=bufs["logits"])
-        if self.greedy_feedback:
-            self._tok_dev[:B].copy_(bufs["logits"].argmax(dim=-1))
-            self._pos_dev[:B] += 1
-        return bufs["logits"]
-
-    def megakernel_error(self, B) -> int:
-        """Non-zero if a bounded wait inside the persistent step kernel expired (synchronises)."""
-        b = self._bufs.get(B)
-        return 0 if b is None else int(b["sync"][1].item())
 
     def _decode_body_unfused(self, B):
         """One launch per operation; serves any batch width."""
@@ -594,27 +586,28 @@ class Transformer(nn.Module):
         """Run one decode step for B branches with the tokens/positions already in the device
         buffers (`_tok_dev`, `_pos_dev`); returns the static logits buffer [B, vocab]."""
         fused = self.use_fused and B <= 16 and self.tp_world == 1
-        mega = self.use_megakernel and B <= 8 and self.tp_world == 1
-        self.launches_per_step = 1 if mega else self.params.n_layers * ((5 if self._fused_attn_for(B) else 7) if fused else 13) + (2 if fused else 1)
+        self.launches_per_step = self.params.n_layers * ((5 if self._fused_attn_for(B) else 7) if fused else 13) + (2 if fused else 1)
         if not self.use_cuda_graph:
             return self._decode_body(B)
-        key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster, self.use_megakernel,
-               self.use_tiled, self.use_fused_attn, self.fused_attn_max_width)
+        key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster, self.use_stream,
+               self.use_tiled, self.use_fused_attn, self.fused_attn_max_width, self.stream_smem_budget)
         g = self._graphs.get(key)
         if g is None:
-            # torch requires capture on a side stream after a warm-up run
+            # torch requires capture on a side stream after a warm-up run; with greedy feedback that run
+            # overwrites the input token and advances the position, so both are put back afterwards
+            tok_saved = self._tok_dev[:B].clone() if self.greedy_feedback else None
             s = torch.cuda.Stream(self.device)
             s.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(s):
                 try:
                     self._decode_body(B)
                 except K.Q40Error:
-                    if not ((fused or mega) and self.max_cluster == 16):
+                    if not (fused and self.max_cluster == 16):
                         raise
                     # this device cannot schedule 16-CTA clusters: use the portable size
                     self.max_cluster = 8
-                    key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster,
-                           self.use_megakernel, self.use_tiled, self.use_fused_attn, self.fused_attn_max_width)
+                    key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster, self.use_stream,
+                           self.use_tiled, self.use_fused_attn, self.fused_attn_max_width, self.stream_smem_budget)
                     self._decode_body(B)
             torch.cuda.current_stream(self.device).wait_stream(s)
             torch.cuda.synchronize(self.device)
@@ -623,11 +616,11 @@ class Transformer(nn.Module):
                 self._decode_body(B)
             self._graphs[key] = g
             if self.greedy_feedback:
-                # the warm-up run advanced the device-side position and token once: undo that
-                # (capture itself executes nothing)
+                # capture itself executes nothing
                 self._pos_dev[:B] -= 1
+                self._tok_dev[:B].copy_(tok_saved)
         g.replay()
-        if self._lm_head_q4 is not None and fused and not mega:
+        if self._lm_head_q4 is not None and fused:
             return self._bufs[B]["logits_pad"][:, :self.params.vocab_size]
         return self._bufs[B]["logits"]
 

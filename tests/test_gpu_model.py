@@ -18,12 +18,12 @@ def small():
     return np.load(os.path.join(ROOT, "tests", "golden", "model_small.npz"))
 
 
-def build_model(g, use_graph):
+def build_model(g, use_graph, max_batch_size=4):
     """Load exactly the way the reference's load_q40.py does: state dict for embedding / norms /
     lm_head, then per-linear assignment of .w / .s / .shape, then model.to(device, fp16)."""
     from spec_mcts_b200.model import ModelArgs, Transformer
     args = ModelArgs(dim=256, n_layers=2, n_heads=2, vocab_size=512, multiple_of=128,
-                     max_batch_size=4, max_seq_len=16, max_prompt_seq_len=32)
+                     max_batch_size=max_batch_size, max_seq_len=16, max_prompt_seq_len=32)
     model = Transformer(args)
     sd = {k[3:]: torch.from_numpy(g[k]) for k in g.files if k.startswith("sd.")}
     model.load_state_dict(sd, strict=False, assign=True)
@@ -125,38 +125,39 @@ def test_small_model_matches_oracle_with_forced_cache(small):
         pos += 1
 
 
-def test_megakernel_matches_multi_kernel_path(small):
-    """The persistent whole-step kernel against the multi-kernel fused path on the same model and
-    inputs: same arithmetic and rounding points, different summation order across CTAs, so logits
-    agree within the matmul tolerance step by step (the Q4_0 cache of the second model is
-    overwritten with the first one's rows after every step, see the forced-cache test above)."""
+@pytest.mark.parametrize("B,use_graph", [(17, True), (32, True), (32, False)])
+def test_wide_step_matches_oracle_with_forced_cache(small, B, use_graph):
+    """Steps of more than 16 branches take the other body of the step driver (one launch per operation,
+    the tcgen05 matmul for all projections, the three-launch tree attention): the same forced-cache
+    comparison with the numpy model oracle as above, on 17 and 32 branches that start from different
+    tokens."""
+    from oracle import model_oracle as MO
+    from oracle import q40_oracle as O
     g = small
-    mega = build_model(g, True)
-    mega.use_megakernel = True
-    ref = build_model(g, True)
-    ref.use_megakernel = False
-    ref.use_tiled = False
-    prompt = torch.from_numpy(g["prompt"]).cuda()
-    l1, l2 = mega(prompt, 0), ref(prompt, 0)
-    assert torch.equal(l1, l2)
-    for B in (1, 3):
-        mega.fork(0, 1, B - 1)
-        ref.fork(0, 1, B - 1)
-        toks = torch.from_numpy(g["first_tokens"][:B]).cuda()
-        pos = prompt.shape[1]
-        for step in range(6):
-            a = mega(toks, pos)[:, -1].float().cpu().numpy()
-            assert mega.megakernel_error(B) == 0
-            b = ref(toks, pos)[:, -1].float().cpu().numpy()
-            logits_close(a, b)
-            for name in ("kq", "ks", "vq", "vs"):
-                ref._caches[name].copy_(mega._caches[name])
-            toks = torch.from_numpy(a.argmax(-1)).view(B, 1).cuda()
-            pos += 1
-        # start the next width from a clean suffix cache
-        for name in ("kq", "ks", "vq", "vs"):
-            mega._caches[name].zero_()
-            ref._caches[name].zero_()
+    model = build_model(g, use_graph, max_batch_size=32)
+    orc = MO.from_golden(g, max_batch_size=32)
+    prompt = g["prompt"]
+    lg = model(torch.from_numpy(prompt).cuda(), 0)
+    lo = orc.forward(prompt, 0)
+    logits_close(lg[0].cpu().numpy(), lo[0])
+    model.fork(0, 1, B - 1)
+    orc.fork(0, 1, B - 1)
+    toks = ((np.arange(B) * 37 + 11) % 512).reshape(B, 1).astype(np.int64)
+    pos = prompt.shape[1]
+    C = model._caches
+    for step in range(5):
+        got = model(torch.from_numpy(toks).cuda(), pos)[:, -1].float().cpu().numpy()
+        assert got.shape == (B, 512)
+        ref = orc.forward(toks, pos)[:, 0]
+        logits_close(got, ref)
+        for l in range(2):
+            for b in range(B):
+                kq, ks = C["kq"][l, b, step].cpu().numpy(), C["ks"][l, b, step].cpu().numpy()
+                vq, vs = C["vq"][l, b, step].cpu().numpy(), C["vs"][l, b, step].cpu().numpy()
+                orc.sk[l][b][step] = O.dequantize_q40(kq, ks.reshape(-1, 1), 64, (2, 128))
+                orc.sv[l][b][step] = O.dequantize_q40(vq, vs.reshape(-1, 1), 64, (2, 128))
+        toks = got.argmax(-1).reshape(B, 1)
+        pos += 1
 
 
 def test_fork_copies_suffix_cache(small):

@@ -1,0 +1,219 @@
+"""Greedy-token parity at the full CodeLlama-7B geometry (32 layers, dim 4096, 32 heads, FFN 11008,
+vocabulary 32016, prompt 512, 32 decode steps, widths 1 and 10) on synthetic N(0, 0.02^2)-like weights
+(tests/synth_model.py), against
+
+  (a) the reference's own model class running its torch path on the same GPU (when the reference
+      files are staged under baseline/_ref by baseline/stage_reference.py; skipped otherwise),
+  (b) tests/golden/model_7b.npz: the same class run on a CPU by tests/golden/make_golden_7b.py,
+  (c) and with the reference's model class, unmodified, running on this repository's drop-in
+      triton_kernels module.
+
+What "identical greedy tokens" can mean here.  With random weights the top-1/top-2 logit margin is
+a fraction of a logit (median 0.2-0.3) and repeatedly falls to one or two fp16 steps of the logits
+(0.0039-0.0078 at |logit| 4-8; exact ties occur), so the arg-max is decided by rounding noise at
+some steps.  The reference does not reproduce its own tokens across hardware: its torch path on a
+B200 differs from its torch path on a CPU at 8 of 320 (step, branch) pairs of the width-10 run
+(all at margins <= 0.023).  The comparison is therefore teacher-forced (every step is fed the
+reference's tokens, so one flipped arg-max does not hide the following steps) and asserts
+  * every step whose reference margin exceeds MARGIN_TOL yields the reference's token,
+  * at least MIN_AGREE of all (step, branch) pairs agree,
+  * for the seed-1 prompt at width 1 (reference margins >= 0.0156 throughout): all 32 tokens
+    identical, which is the same statement as 32 identical free-running greedy tokens.
+The bounds are tighter for the kernels that keep the reference's operand rounding, fp16(code*scale)
+(`use_tiled = False`), than for the default decode path, which rounds fp16(scale*x) instead (both
+are one rounding per product; see q40_gemv_tiled.cu) and therefore flips more 4-bit codes of the
+quantised KV cache relative to the reference's run.
+"""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+import ref_loader as RL  # noqa: E402
+import synth_model as SM  # noqa: E402
+
+STEPS, PROMPT, WIDTH = 32, 512, 10
+# (largest reference margin at which a token may differ, smallest fraction of agreeing pairs)
+BOUNDS = {"default": (0.5, 0.90), "reference_rounding": (0.05, 0.95)}
+
+
+@pytest.fixture(scope="module")
+def ours():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from spec_mcts_b200 import kernels as K
+    from spec_mcts_b200.model import ModelArgs, Transformer
+    args = ModelArgs(max_batch_size=16, max_seq_len=STEPS + 8, max_prompt_seq_len=PROMPT)
+    m = Transformer(args)
+    hidden = m.layers[0].feed_forward.hidden_dim
+    assert (args.dim, args.n_layers, args.n_heads, hidden, args.vocab_size) == (4096, 32, 32, 11008, 32016)
+    digest = SM.load_synthetic(m, K.quantize_q40, 0, 4096, 32, 32, hidden, 32016, "cuda")
+    m = m.to("cuda", torch.float16)
+    m.synthetic_digest = digest
+    return m
+
+
+def build_reference(ours_model, flavour):
+    """The reference's Transformer on the same tensors as `ours_model`, loaded the way load_q40.py does."""
+    M = RL.reference_model(flavour)
+    p = ours_model.params
+    m = M.Transformer(M.ModelArgs(max_batch_size=p.max_batch_size, max_seq_len=p.max_seq_len,
+                                  max_prompt_seq_len=p.max_prompt_seq_len))
+    sd = {"tok_embeddings.weight": ours_model.tok_embeddings.weight.data,
+          "output.weight": ours_model.output.weight.data, "norm.weight": ours_model.norm.weight.data}
+    for i, l in enumerate(ours_model.layers):
+        sd[f"layers.{i}.attention_norm.weight"] = l.attention_norm.weight.data
+        sd[f"layers.{i}.ffn_norm.weight"] = l.ffn_norm.weight.data
+    m.load_state_dict(sd, strict=False, assign=True)
+    for lo, lr in zip(ours_model.layers, m.layers):
+        for grp, names in (("attention", ("wq", "wk", "wv", "wo")), ("feed_forward", ("w1", "w2", "w3"))):
+            for n in names:
+                a, b = getattr(getattr(lo, grp), n), getattr(getattr(lr, grp), n)
+                b.w, b.s, b.shape = a.w, a.s, a.shape
+    m.to(device="cuda", dtype=torch.float16)
+    return m
+
+
+def reset(m):
+    if hasattr(m, "_caches"):
+        for n in ("kq", "ks", "vq", "vs"):
+            m._caches[n].zero_()
+    else:
+        for l in m.layers:
+            a = l.attention
+            a.cache_k.zero_(); a.cache_k_s.zero_(); a.cache_v.zero_(); a.cache_v_s.zero_()
+    m.resetSeq()
+
+
+def reference_run(ref, prompt, width):
+    """Free-running greedy decode of the reference: tokens [STEPS, width] and margins."""
+    reset(ref)
+    lg = ref(prompt, 0)[0, -1].float()
+    first = torch.topk(lg, width).indices.view(width, 1)
+    if width > 1:
+        ref.fork(0, 1, width - 1)
+    toks, pos, tk, mg = first, prompt.shape[1], [], []
+    for _ in range(STEPS):
+        l = ref(toks, pos)[:, -1].float()
+        top = torch.topk(l, 2, dim=-1)
+        toks = top.indices[:, :1].clone()
+        tk.append(toks[:, 0].clone())
+        mg.append(top.values[:, 0] - top.values[:, 1])
+        pos += 1
+    return first, torch.stack(tk), torch.stack(mg)
+
+
+def teacher_forced(m, prompt, first, ref_tokens, width):
+    reset(m)
+    m(prompt, 0)
+    if width > 1:
+        m.fork(0, 1, width - 1)
+    toks, pos, out = first, prompt.shape[1], []
+    for s in range(STEPS):
+        out.append(m(toks, pos)[:, -1].float().argmax(-1))
+        toks = ref_tokens[s].view(width, 1)
+        pos += 1
+    return torch.stack(out)
+
+
+def check(got, ref_tokens, margins, bounds, what):
+    mism = (got != ref_tokens)
+    bad = margins[mism]
+    n, tot = int(mism.sum()), mism.numel()
+    print(f"{what}: {tot - n} of {tot} (step, branch) tokens identical; reference margins at the others "
+          f"{[round(float(x), 4) for x in bad]}; smallest margin of the run {float(margins.min()):.4f}")
+    tol, agree = bounds
+    assert n == 0 or float(bad.max()) <= tol, (what, "token differs at reference margin", float(bad.max()))
+    assert (tot - n) / tot >= agree, (what, tot - n, tot)
+    return n
+
+
+def set_path(m, path):
+    m.use_tiled = path == "default"
+
+
+def seeded_prompt(seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, 32016, (1, PROMPT), generator=g).cuda()
+
+
+@pytest.fixture(scope="module")
+def ref_gpu(ours):
+    if not RL.available():
+        pytest.skip("reference files not staged under baseline/_ref (python baseline/stage_reference.py <checkout>)")
+    return build_reference(ours, "torch")
+
+
+@pytest.mark.parametrize("path", ["default", "reference_rounding"])
+def test_7b_tokens_against_reference_class_on_gpu(ours, ref_gpu, path):
+    """(a): the reference class (torch path) and this repository's model on the same GPU."""
+    with torch.inference_mode():
+        for seed, width in ((1, 1), (0, WIDTH)):
+            prompt = seeded_prompt(seed)
+            first, ref_tokens, margins = reference_run(ref_gpu, prompt, width)
+            set_path(ours, path)
+            got = teacher_forced(ours, prompt, first, ref_tokens, width)
+            n = check(got, ref_tokens, margins, BOUNDS[path], f"{path}, prompt seed {seed}, width {width}")
+            if width == 1:
+                assert n == 0, "32 greedy tokens of the width-1 run must be identical"
+    set_path(ours, "default")
+
+
+@pytest.mark.parametrize("relayout", [True, False])
+def test_7b_reference_class_runs_unchanged_on_the_drop_in_kernels(ours, ref_gpu, relayout):
+    """(c): hf_model_q40_kv_shared.Transformer imported against this repository's triton_kernels.py —
+    its forward, fork and cache handling untouched — against the same class on its own torch path."""
+    from spec_mcts_b200 import kernels as K
+    shim = build_reference(ours, "shim")
+    assert RL.reference_model("shim").matmul_q40 is K.matmul_q40
+    K.relayout_cache_config(enabled=relayout)
+    try:
+        with torch.inference_mode():
+            prompt = seeded_prompt(1)
+            first, ref_tokens, margins = reference_run(ref_gpu, prompt, 1)
+            got = teacher_forced(shim, prompt, first, ref_tokens, 1)
+            check(got, ref_tokens, margins, BOUNDS["default" if relayout else "reference_rounding"],
+                  f"reference class on the drop-in kernels (tiled copies {relayout}), width 1")
+            prompt = seeded_prompt(0)
+            first, ref_tokens, margins = reference_run(ref_gpu, prompt, WIDTH)
+            got = teacher_forced(shim, prompt, first, ref_tokens, WIDTH)
+            check(got, ref_tokens, margins, BOUNDS["default" if relayout else "reference_rounding"],
+                  f"reference class on the drop-in kernels (tiled copies {relayout}), width {WIDTH}")
+    finally:
+        K.relayout_cache_config(enabled=True, clear=True)
+        del shim
+
+
+@pytest.mark.parametrize("path", ["default", "reference_rounding"])
+def test_7b_tokens_against_cpu_golden_of_the_reference_class(ours, path):
+    """(b): the committed vectors of the reference class run on a CPU (prompt seed 0).  The CPU and GPU
+    BLAS sum in different orders, so these bounds also cover the reference against itself."""
+    G = np.load(os.path.join(HERE, "golden", "model_7b.npz"))
+    assert str(G["weights_sha256"]) == ours.synthetic_digest, "synthetic weights differ from the generator's"
+    assert int(G["n_layers"]) == 32
+    prompt = torch.from_numpy(G["prompt"]).cuda()
+    set_path(ours, path)
+    with torch.inference_mode():
+        for width, tag in ((1, "w1"), (WIDTH, "w10")):
+            ref_tokens = torch.from_numpy(G[f"{tag}.tokens"]).cuda()
+            tv = torch.from_numpy(G[f"{tag}.top_values"].astype(np.float32)).cuda()
+            margins = tv[..., 0] - tv[..., 1]
+            first = torch.from_numpy(G["first_tokens"][:width]).view(width, 1).cuda()
+            reset(ours)
+            lg = ours(prompt, 0)[0, -1].float().cpu().numpy()
+            # prefill logits: rel 2e-2 / abs 5e-2 (512 positions through 32 layers, fp16 logits of size ~5)
+            np.testing.assert_allclose(lg, G["prefill_logits_last"].astype(np.float32), rtol=2e-2, atol=5e-2)
+            if width > 1:
+                ours.fork(0, 1, width - 1)
+            toks, pos, out = first, PROMPT, []
+            for s in range(STEPS):
+                out.append(ours(toks, pos)[:, -1].float().argmax(-1))
+                toks = ref_tokens[s].view(width, 1)
+                pos += 1
+            check(torch.stack(out), ref_tokens, margins, BOUNDS[path], f"{path} vs CPU golden, width {width}")
+    set_path(ours, "default")
