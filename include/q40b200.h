@@ -157,9 +157,9 @@ size_t q40_tiled_bytes(int N, int K);
 int q40_relayout_tiled(const void* bw, const void* bs, void* out, int N, int K, void* stream);
 
 /* q40_gemv_fused on tiled copies (same modes, arguments and results up to rounding: the scale is
- * applied to the activations, fp16(scale*x), instead of to the weight, and in modes 1 and 3 the
- * row's 1/rms multiplies the finished fp32 sums instead of the activations; 1 <= M <= 16; every
- * N % 256 == 0).  bw[i] are the tiled streams; bs is ignored and may be NULL. */
+ * applied to the activations, fp16(scale*x), instead of to the weight; the RMSNorm of modes 1 and 3
+ * keeps the reference's rounding points; 1 <= M <= 16; every N % 256 == 0).  bw[i] are the tiled
+ * streams; bs is ignored and may be NULL. */
 int q40_gemv_tiled(int mode, int nmat, const void* const* bw, const void* const* bs, void* const* out,
                    const int* n_cols, int64_t ldc, const void* a, int64_t lda, int M, int K,
                    const void* norm_w, const float* ss_in, int ss_in_count, float eps, const void* h_in,

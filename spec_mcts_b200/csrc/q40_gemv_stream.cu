@@ -357,7 +357,8 @@ __global__ void __launch_bounds__(THREADS, MT == 1 ? 2 : 1) gemv_stream_kernel(c
 #ifdef Q40_TRACE
       const long long tf0_ = clock64();
 #endif
-      float* sl = slab + (seg & 1) * (4 * p.M * SPAN_COLS);      // double-buffered: one barrier per span
+      // double-buffered up to 8 rows (one barrier per span); above, one buffer and a second barrier
+      float* sl = slab + ((MT == 1) ? (seg & 1) * (4 * p.M * SPAN_COLS) : 0);
       // the accumulator fragment of a lane holds batch rows 2t, 2t+1; their sums of scale * x sit, split over
       // the four lanes of a quad, in the lanes whose g is that batch row
       float corr[MT][2][2];
@@ -392,6 +393,7 @@ __global__ void __launch_bounds__(THREADS, MT == 1 ? 2 : 1) gemv_stream_kernel(c
         for (int s4 = 0; s4 < 4; ++s4) v += sl[(s4 * p.M + m) * SPAN_COLS + tid];
         part[m * SPAN_COLS + tid] = v;
       }
+      if (MT != 1) bar_consumers();
 #ifdef Q40_TRACE
       if (threadIdx.x == 0) q40_ts_[3] += (unsigned long long)(clock64() - tf0_);
 #endif
@@ -522,7 +524,7 @@ static int launch(Params& p, const Plan& pl, int smem_budget, cudaStream_t st, b
   int xs_ld = per * 16;
   xs_ld = (xs_ld + 63) / 64 * 64 + 16;
   const size_t xs_bytes = (size_t)xs_rows * xs_ld * 2;
-  const size_t slab_bytes = (size_t)2 * 4 * p.M * SPAN_COLS * 4;
+  const size_t slab_bytes = (size_t)(MT == 1 ? 2 : 1) * 4 * p.M * SPAN_COLS * 4;
   const size_t misc_bytes = 16 * 4 + 128 * 4 + 16 + (size_t)((pl.nseg_max + 3) / 4 * 4) * 4;
   if (pl.nseg_max > CONS_THREADS) return Q40_E_UNSUPPORTED;
   const int slots_needed = (per + SLOT_STEPS - 1) / SLOT_STEPS + pl.nseg_max;

@@ -1,5 +1,5 @@
 // Decode-step Q4_0 matmul on a re-laid-out copy of the weights ("tiled" format): the same
-// launch structure as q40_gemv_tiled.cu (cp.async ring, programmatic dependent launch, cluster
+// launch structure as q40_gemv_fused.cu (cp.async ring, programmatic dependent launch, cluster
 // split-K through distributed shared memory, RMSNorm prologue, residual / SiLU-mul epilogues)
 // with an inner loop of about one instruction per weight instead of almost three.
 //
@@ -58,9 +58,8 @@ struct TiledParams {
   const __half* a;     // [M, lda] activations; with PRO_NORM the un-normalised residual stream
   int64_t lda, ldc;
   int M, K, rows_per_split;
-  // PRO_NORM: the activations are fp16(a * norm_w) and every finished sum is multiplied by
-  // rsqrt(sum(ss_in[m][:]) / K + eps) in fp32 (the reference rounds fp16(fp16(a * rsqrt(..)) * norm_w)
-  // before the matmul; the difference is one fp16 rounding of the operand, like the scale placement)
+  // PRO_NORM: the activations are fp16(fp16(float(a) * rsqrt(sum(ss_in[m][:]) / K + eps)) * norm_w), the
+  // reference's RMSNorm (hf_model_q40_kv_shared.py:129-134)
   const __half* norm_w;
   const float* ss_in;
   int ss_in_count;
@@ -182,28 +181,35 @@ gemv_tiled_kernel(const TiledParams p) {
   if (EPI == EPI_RESIDUAL && warp < p.M && lane < slice && col_ok)
     h_first = p.h_in[(int64_t)warp * p.ldh + f_span_col(span, rank * slice + lane)];
 
-  // ---- activations of this k range: raw copy first (and the norm weights), so that the loads do
-  // not wait for the row statistics; then, for the RMSNorm prologue, normalise in place ----
+  // ---- activations of this k range.  RMSNorm prologue with the reference's rounding points:
+  // fp16(fp16(float(a) * 1/rms) * norm_w).  The raw values are requested first, then the row statistics
+  // are summed while they are in flight ----
   {
     const int chunks = p.rows_per_split / 8;
-    for (int idx = tid; idx < MT * 8 * chunks; idx += FT) {
+    const int total = MT * 8 * chunks;
+    auto load_chunk = [&](int idx) {
+      const int m = idx / chunks, k = kb + (idx % chunks) * 8;
+      return (m < p.M && k < ke) ? *reinterpret_cast<const uint4*>(p.a + (int64_t)m * p.lda + k)
+                                 : make_uint4(0, 0, 0, 0);
+    };
+    auto store_chunk = [&](int idx, uint4 v) {
       const int m = idx / chunks, kk = (idx % chunks) * 8;
-      uint4 v = make_uint4(0, 0, 0, 0);
       const int k = kb + kk;
-      if (m < p.M && k < ke) {
-        v = *reinterpret_cast<const uint4*>(p.a + (int64_t)m * p.lda + k);
-        if (PRO == PRO_NORM) {
-          // RMSNorm prologue: the norm weight is applied here, the row's 1/rms (a scalar per row) to
-          // the finished sums in the epilogue, so that nothing at the start of the launch waits for it
-          const uint4 wv = *reinterpret_cast<const uint4*>(p.norm_w + k);
-          __half2* vh = reinterpret_cast<__half2*>(&v);
-          const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+      if (PRO == PRO_NORM && m < p.M && k < ke) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(p.norm_w + k);
+        const float inv = s_inv[m];
+        __half2* vh = reinterpret_cast<__half2*>(&v);
+        const __half2* wh = reinterpret_cast<const __half2*>(&wv);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) vh[j] = __hmul2(vh[j], wh[j]);
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(vh[j]);
+          vh[j] = __hmul2(__floats2half2_rn(f.x * inv, f.y * inv), wh[j]);
         }
       }
       *reinterpret_cast<uint4*>(xs + m * xs_ld + kk) = v;
-    }
+    };
+    uint4 v_first = make_uint4(0, 0, 0, 0);
+    if (tid < total) v_first = load_chunk(tid);
     if (PRO == PRO_NORM) {
       for (int m = warp; m < p.M; m += FW) {
         // all loads in flight before the first add (the partials sit in L2)
@@ -222,7 +228,10 @@ gemv_tiled_kernel(const TiledParams p) {
         s = warp_sum(s);
         if (lane == 0) s_inv[m] = rsqrtf(s / (float)p.K + p.eps);
       }
+      __syncthreads();
     }
+    if (tid < total) store_chunk(tid, v_first);
+    for (int idx = tid + FT; idx < total; idx += FT) store_chunk(idx, load_chunk(idx));
   }
   __syncthreads();
 
@@ -333,7 +342,6 @@ gemv_tiled_kernel(const TiledParams p) {
   const int npart = (EPI == EPI_SILU) ? nranks / 2 : nranks;
   for (int m = warp; m < p.M; m += FW) {
     float ssq = 0.f;
-    const float inv = (PRO == PRO_NORM) ? s_inv[m] : 1.0f;
     for (int cidx = lane; cidx < slice; cidx += 32) {
       const int lc = rank * slice + cidx;
       const float* rp = recv + m * slice + cidx;
@@ -347,7 +355,6 @@ gemv_tiled_kernel(const TiledParams p) {
       } else {
         for (int r = 0; r < npart; ++r) v0 += rp[r * rstride];
       }
-      if (PRO == PRO_NORM) { v0 *= inv; v1 *= inv; }
       const int n = f_span_col(span, lc);
       if (n < pr.N) {
         if (EPI == EPI_STORE) {

@@ -19,10 +19,11 @@ reference's tokens, so one flipped arg-max does not hide the following steps) an
   * at least MIN_AGREE of all (step, branch) pairs agree,
   * for the seed-1 prompt at width 1 (reference margins >= 0.0156 throughout): all 32 tokens
     identical, which is the same statement as 32 identical free-running greedy tokens.
-The bounds are tighter for the kernels that keep the reference's operand rounding, fp16(code*scale)
-(`use_tiled = False`), than for the default decode path, which rounds fp16(scale*x) instead (both
-are one rounding per product; see q40_gemv_tiled.cu) and therefore flips more 4-bit codes of the
-quantised KV cache relative to the reference's run.
+The margin bound is tighter for the kernels that keep the reference's operand rounding,
+fp16(code*scale) (`use_tiled = False`), than for the default decode path, which rounds fp16(scale*x)
+instead (both are one rounding per product; see q40_gemv_tiled.cu): measured on a B200, the default
+path differs from the reference at 7 of 320 pairs of the width-10 run (largest margin 0.05), the
+reference-rounding path at 8 of 320 (largest margin 0.027), the reference's CPU run at 8 of 320.
 """
 import os
 import sys
@@ -39,7 +40,7 @@ import synth_model as SM  # noqa: E402
 
 STEPS, PROMPT, WIDTH = 32, 512, 10
 # (largest reference margin at which a token may differ, smallest fraction of agreeing pairs)
-BOUNDS = {"default": (0.5, 0.90), "reference_rounding": (0.05, 0.95)}
+BOUNDS = {"default": (0.2, 0.95), "reference_rounding": (0.05, 0.95)}
 
 
 @pytest.fixture(scope="module")
