@@ -110,11 +110,21 @@ int q40_gemm_kn_tc_multi(int nmat, const void* a, int64_t lda, const void* const
  * a problem whose q40_gemm_workspace_bytes() exceeds it returns Q40_E_WORKSPACE.  The first
  * call on a device looks up the array's device address and should precede any stream
  * capture.  Calls share the array, so calls that overlap on the GPU race; calls on one
- * stream are safe.  No allocation is made by this entry point or anything it calls.
+ * stream are safe (host threads may make the first call on a device concurrently).  The array of the
+ * CURRENT device is used: make the device of `stream` current before the call.  No allocation is made
+ * by this entry point or anything it calls.
  * This entry point has no counterpart in the reference. */
 int q40_gemm_kn_static(const void* a, int64_t lda, const void* bw, const void* bs, void* c,
                        int64_t ldc, int M, int N, int K, int group, void* stream);
 size_t q40_gemm_kn_static_max_workspace(void);
+/* Above 16 rows q40_gemm_kn_static runs the tcgen05 kernel, whose bounded waits report expiry in a
+ * word inside the library's array: this copies that word to *host_out (0 = every call since the last
+ * clear completed its waits; non-zero = at least one output is undefined), optionally clears it, and
+ * waits for `stream`.  It is this library's status read-back for the entry points that own no
+ * caller-visible workspace; with a caller-owned workspace the same word is the int at byte 4092 of the
+ * workspace (q40_gemm_kn) or the `err` argument (q40_gemm_kn_tc), and q40_gemv_stream reports in the
+ * first int of its workspace.  No counterpart in the reference. */
+int q40_gemm_kn_static_error(int* host_out, int clear, void* stream);
 
 /* Y[M,N] = X[M,K] @ deq(W)[N,K]^T, W quantised from a row-major [N,K] matrix (groups
  * along K): wq viewed as [N*K/(2*group), group], ws as [N*K/group].  K % (2*group) == 0.

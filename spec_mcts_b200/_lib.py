@@ -49,6 +49,7 @@ SIGNATURES = {
     "q40_gemm_kn_static": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
                                    c_int, c_int, c_void_p]),
     "q40_gemm_kn_static_max_workspace": (c_size_t, []),
+    "q40_gemm_kn_static_error": (c_int, [c_void_p, c_int, c_void_p]),
     "q40_gemm_nk": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
                             c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "q40_gemv_fused": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64,

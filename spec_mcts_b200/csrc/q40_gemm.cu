@@ -20,6 +20,8 @@
 // k reduction in fp32, warps are summed through shared memory and CTAs (split-K) through
 // an fp32 workspace where the last CTA to arrive adds the partials in a fixed order, so
 // results do not depend on scheduling.
+#include <atomic>
+
 #include "q40_common.cuh"
 
 namespace q40 {
@@ -629,35 +631,61 @@ extern "C" int q40_gemm_nk(const void* x, int64_t ldx, const void* wq, const voi
 // All calls share the one array: the arrival counters at its start are cleared on the
 // stream before every launch, the partial sums behind them are fully overwritten before
 // they are read, and two calls that overlap on the GPU (different streams) would race.
+// The array is picked by the CURRENT device (cudaGetDevice), which must be the device `stream`
+// belongs to.  Above 16 rows the tcgen05 kernel reports an expired bounded wait in the last word of
+// the array's 4096-byte header; q40_gemm_kn_static_error copies that word to the host.
 // Nothing here calls cudaMalloc, cudaFree or any allocating library routine.
 // ---------------------------------------------------------------------------------------
 #define Q40_STATIC_WS_BYTES (8u * 1024u * 1024u)
 
 static __device__ __align__(256) unsigned char q40_static_ws[Q40_STATIC_WS_BYTES];
 
-static void* q40_static_ws_ptr[64];       // device address of the array, per device ordinal
-static bool q40_static_ws_ready[64];
+// device address of the array per device ordinal; null = not looked up yet.  Two host threads that make
+// the first call on a device at the same time both resolve the same address; the store/load pair only
+// makes that formally race-free.
+static std::atomic<void*> q40_static_ws_ptr[64];
 
 extern "C" size_t q40_gemm_kn_static_max_workspace(void) { return (size_t)Q40_STATIC_WS_BYTES; }
+
+static int q40_static_ws_lookup(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return Q40_E_UNSUPPORTED;
+  void* ptr = q40_static_ws_ptr[dev].load(std::memory_order_acquire);
+  if (!ptr) {
+    e = cudaGetSymbolAddress(&ptr, q40_static_ws);
+    if (e != cudaSuccess) return (int)e;
+    q40_static_ws_ptr[dev].store(ptr, std::memory_order_release);
+  }
+  *out = ptr;
+  return Q40_OK;
+}
 
 extern "C" int q40_gemm_kn_static(const void* a, int64_t lda, const void* bw, const void* bs, void* c,
                                   int64_t ldc, int M, int N, int K, int group, void* stream) {
   if (M > 0 && N > 0 && K > 0 && q40_gemm_workspace_bytes(M, N, K) > (size_t)Q40_STATIC_WS_BYTES)
     return Q40_E_WORKSPACE;
-  int dev = -1;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return (int)e;
-  if (dev < 0 || dev >= 64) return Q40_E_UNSUPPORTED;
-  if (!q40_static_ws_ready[dev]) {
-    void* ptr = nullptr;
-    e = cudaGetSymbolAddress(&ptr, q40_static_ws);
-    if (e != cudaSuccess) return (int)e;
-    q40_static_ws_ptr[dev] = ptr;
-    q40_static_ws_ready[dev] = true;
-  }
-  void* ws = q40_static_ws_ptr[dev];
-  // the counters must read zero when a launch starts, whatever an earlier call left behind
-  e = cudaMemsetAsync(ws, 0, q40::COUNTER_BYTES, (cudaStream_t)stream);
+  void* ws = nullptr;
+  const int rc = q40_static_ws_lookup(&ws);
+  if (rc != Q40_OK) return rc;
+  // the arrival counters must read zero when a launch starts, whatever an earlier call left behind; the
+  // last word of the header is the tensor-core kernel's error word (above 16 rows), which is sticky: it
+  // is read and cleared only through q40_gemm_kn_static_error
+  const cudaError_t e = cudaMemsetAsync(ws, 0, q40::COUNTER_BYTES - 4, (cudaStream_t)stream);
   if (e != cudaSuccess) return (int)e;
   return q40_gemm_kn(a, lda, bw, bs, c, ldc, M, N, K, group, ws, (size_t)Q40_STATIC_WS_BYTES, stream);
+}
+
+extern "C" int q40_gemm_kn_static_error(int* host_out, int clear, void* stream) {
+  if (!host_out) return Q40_E_NULL;
+  void* ws = nullptr;
+  const int rc = q40_static_ws_lookup(&ws);
+  if (rc != Q40_OK) return rc;
+  char* word = (char*)ws + q40::COUNTER_BYTES - 4;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaMemcpyAsync(host_out, word, 4, cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess && clear) e = cudaMemsetAsync(word, 0, 4, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  return e == cudaSuccess ? Q40_OK : (int)e;
 }

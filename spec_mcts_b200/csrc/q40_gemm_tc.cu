@@ -357,7 +357,11 @@ static TcKernel tc_kernel_for(int mpad) {
   return q40::gemm_tc_kernel<256, 2>;
 }
 static int tc_max_clusters(TcKernel kern, int mpad, int nsplit, size_t smem) {
-  static int cache[9][17] = {};          // [nsplit][padded rows / 16] -> fit + 1 (the shared memory size follows from the rows)
+  // [device][nsplit][padded rows / 16] -> fit + 1 (the shared memory size follows from the rows)
+  static int cache_all[16][9][17] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) dev = 0;
+  int (*cache)[17] = cache_all[dev];
   const int cls = mpad / 16;
   if (cache[nsplit][cls]) return cache[nsplit][cls] - 1;
   cudaLaunchConfig_t cfg{};

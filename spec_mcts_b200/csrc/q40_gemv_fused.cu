@@ -346,8 +346,13 @@ static int launch_fused(const FusedParams& p, int grid_x, int nsplit, int cluste
   const size_t xs = (size_t)MT * 8 * (p.rows_per_split + F_XS_PAD) * 2 + 64 + (size_t)p.rows_per_split * 2;
   const size_t red = (size_t)FW * MT * 16 * 32 * 16 + (size_t)p.M * F_SPAN_COLS * 4;
   const size_t smem = (ring + xs) > red ? (ring + xs) : red;
+  // a shape whose shared-memory need exceeds what a CTA of this device may have is refused with a
+  // negative status (callers fall back to the workspace kernel), not reported as a CUDA error
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return (int)e;
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return Q40_E_UNSUPPORTED;
+  }
   if (cluster_x * nsplit > 8) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return (int)e;

@@ -393,8 +393,13 @@ static int launch_tiled(const TiledParams& p, int grid_x, int nsplit, int cluste
   TiledParams pp = p;
   pp.recv_off = (int)smem;
   smem += (size_t)p.M * F_SPAN_COLS * 4;        // receive buffer of the cluster reduction
+  // a shape whose shared-memory need exceeds what a CTA of this device may have is refused with a
+  // negative status (callers fall back to the workspace kernel), not reported as a CUDA error
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return (int)e;
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return Q40_E_UNSUPPORTED;
+  }
   // set on every variant, not only those that need it (see the note at q40_gemv_tiled)
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
   if (e != cudaSuccess) return (int)e;

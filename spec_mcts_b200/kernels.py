@@ -42,6 +42,11 @@ def _need_cuda(*ts: torch.Tensor) -> torch.device:
             dev = t.device
         elif t.device != dev:
             raise Q40Error(f"tensors on different devices: {dev} and {t.device}")
+    if dev is not None and dev.index != torch.cuda.current_device():
+        # the library launches on the current device (and keeps per-device state by it): refuse instead
+        # of failing inside CUDA with an invalid resource handle
+        raise Q40Error(f"tensors live on {dev} but the current CUDA device is {torch.cuda.current_device()}: "
+                       f"wrap the call in `with torch.cuda.device({dev.index}):`")
     return dev
 
 
