@@ -16,8 +16,12 @@ Printed line (rank 0): the driver's JSON contract, plus
                 sample: the 7 linears of one layer, extrapolated to a token
   e2e           the same metric through model(tokens, start_pos) with host tokens in pinned
                 memory copied in and the argmax token ids copied out every step
+  kernels       (N = 1) the kernel-level configurations: the isolated 4096 x 4096 Q4_0 GEMV at batch 1
+                (GB/s against the measured and the nominal 8 TB/s peak) and the shared-prefix tree attention
+  tp_70b        (N > 1) CodeLlama-70B-architecture decode, tensor parallel over the N ranks
 With N > 1 the 7B path does not shard: every rank runs an independent replica
-(scaling "weak"), value is the sum over replicas divided by the slowest replica's time.
+(scaling "weak"), value is the sum over replicas divided by the slowest replica's time; the 70B
+geometry, which does shard, is measured afterwards on the same ranks and reported in `tp_70b`.
 """
 from __future__ import annotations
 
@@ -42,9 +46,20 @@ N_LAYERS, DIM, HEADS, FFN, VOCAB = 32, 4096, 32, 11008, 32016
 LAYER_SHAPES = [(4096, 4096)] * 4 + [(11008, 4096), (11008, 4096), (4096, 11008)]   # (N, K): q k v o w1 w3 w2
 
 
-# ncu dram__bytes_read.sum + dram__bytes_write.sum of the four tiled matmul launches of one 7B layer
-# at width 1, averaged per launch (filled in from the capture under profiles/)
-TILED_TRAFFIC_PER_LAUNCH = 26.9e6
+def measured_traffic(kernel_prefix):
+    """DRAM read + write bytes per average launch of the dominant kernel, as recorded by the profiler
+    capture whose summary is kept with the sources (a line `traffic_bytes_per_launch[<kernel>]: <bytes>`);
+    None when no capture of that kernel is on record."""
+    import glob
+    import re
+    for path in sorted(glob.glob(os.path.join(ROOT, "profiles", "*.md"))):
+        try:
+            m = re.search(r"traffic_bytes_per_launch\[%s\]:\s*([0-9.eE+]+)" % re.escape(kernel_prefix), open(path).read())
+        except OSError:
+            continue
+        if m:
+            return float(m.group(1))
+    return None
 
 
 def q4_bytes(n, k, m, group=64):
@@ -127,28 +142,63 @@ def cpu_layer_sample(width, threads, repeats):
     return times[len(times) // 2], deq_t / repeats, mm_t / repeats
 
 
+def workload_config(widths, world, skip_prefill):
+    w0 = widths[0]
+    return {"workload": "codellama-7b-arch q4_0 decode (32 layers, hidden 4096, ffn 11008, vocab 32016), "
+                        "random-init N(0,0.02^2) weights, prompt 512 shared, greedy, width %d" % w0,
+            "group": 64, "prompt_len": PROMPT_LEN, "widths": widths, "replicas": world,
+            "skip_prefill": bool(skip_prefill),
+            "l2": "inputs larger than L2 (3.7 GB of weights streamed per step)"}
+
+
 def run_reference_arm(args):
     """`--impl reference`: the reference's own CPU implementation of the path (restated in
     oracle/cpu_path.py; the reference is Python and does not travel to the GPU box), all host
-    threads.  One step = the Q4_0 linears of one layer at batch 1; tokens/s extrapolates
-    to 32 layers (attention, norms and the fp16 lm_head are left out, which favours the CPU)."""
+    threads.  One step = a bounded sample of a decode step at width 1: the seven Q4_0 linears of
+    one layer (of 32; attention, norms and the fp16 lm_head are left out, which favours the CPU);
+    tokens/s extrapolates the sample to 32 layers.  W untimed and K timed steps, as asked."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    import torch
+    from oracle import cpu_path as C
     threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
     steps, warm = max(args.steps, 1), max(args.warmup, 0)
-    steps = min(steps, 20)          # bounded: one step is ~0.3-1 s of CPU work
-    t_layer, td, tm = cpu_layer_sample(1, threads, steps)
+    g = torch.Generator().manual_seed(0)
+    by_shape = {}
+    for (n, k) in sorted(set(LAYER_SHAPES)):
+        wt = (torch.randn((k, n), generator=g) * 0.02).to(torch.float16)
+        by_shape[(n, k)] = C.quantize(wt, 64)
+    xs = {k: torch.randn((1, k), generator=g).to(torch.float16) for k in (4096, 11008)}
+
+    def step():
+        td = tm = 0.0
+        for (n, k) in LAYER_SHAPES:
+            q, sc = by_shape[(n, k)]
+            _, a, b = C.linear_kn(xs[k], q, sc, (k, n))
+            td += a; tm += b
+        return td, tm
+
+    for _ in range(warm):
+        step()
+    t0 = time.perf_counter()
+    td = tm = 0.0
+    for _ in range(steps):
+        a, b = step()
+        td += a; tm += b
+    t_layer = (time.perf_counter() - t0) / steps
     value = 1.0 / (t_layer * N_LAYERS)
+    widths = [int(w) for w in args.widths.split(",")]
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": steps, "warmup": 1, "ms_per_step": t_layer * 1e3, "higher_is_better": True,
+        "steps": steps, "warmup": warm, "ms_per_step": t_layer * N_LAYERS * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "codellama-7b-arch q4_0 decode, width 1, prompt 512 (CPU: linears of one layer per step, x32)",
-                   "group": 64},
+        "config": workload_config(widths, max(args.gpus, 1), args.skip_prefill),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": "7 Q4_0 linears of one layer (torch unpack + matmul), median of %d, x32 layers; "
-                                   "unpack %.1f ms + matmul %.1f ms per layer" % (steps, td * 1e3, tm * 1e3)},
+                         "sample": "per step the 7 Q4_0 linears of one layer at batch 1 (torch unpack %.1f ms + matmul "
+                                   "%.1f ms), x32 layers; attention/norms/lm_head not counted"
+                                   % (td / steps * 1e3, tm / steps * 1e3)},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -247,6 +297,55 @@ def timed_e2e(model, width, steps, warmup, prompt_len):
     return e0.elapsed_time(e1) * 1e-3, width * 8, width * 8
 
 
+def reference_class_on_drop_in(model, dev, steps=16):
+    """tokens/s at width 1 of the reference's own Transformer class (when its files are staged under
+    baseline/_ref), imported against this repository's triton_kernels module and given this model's
+    tensors: what the reference's per-operation Python loop costs on the same kernels."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    try:
+        import ref_loader as RL
+    except ImportError:
+        return None
+    if not RL.available():
+        return None
+    M = RL.reference_model("shim")
+    p = model.params
+    ref = M.Transformer(M.ModelArgs(max_batch_size=1, max_seq_len=p.max_seq_len, max_prompt_seq_len=p.max_prompt_seq_len))
+    sd = {"tok_embeddings.weight": model.tok_embeddings.weight.data, "output.weight": model.output.weight.data,
+          "norm.weight": model.norm.weight.data}
+    for i, l in enumerate(model.layers):
+        sd[f"layers.{i}.attention_norm.weight"] = l.attention_norm.weight.data
+        sd[f"layers.{i}.ffn_norm.weight"] = l.ffn_norm.weight.data
+    ref.load_state_dict(sd, strict=False, assign=True)
+    for lo, lr in zip(model.layers, ref.layers):
+        for grp, names in (("attention", ("wq", "wk", "wv", "wo")), ("feed_forward", ("w1", "w2", "w3"))):
+            for n in names:
+                a, b = getattr(getattr(lo, grp), n), getattr(getattr(lr, grp), n)
+                b.w, b.s, b.shape = a.w, a.s, a.shape
+    ref.to(device=dev, dtype=torch.float16)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, VOCAB, (1, PROMPT_LEN), generator=g).to(dev)
+    tok = ref(prompt, 0)[:, -1].argmax(-1, keepdim=True)
+    pos = PROMPT_LEN
+    for _ in range(3):
+        tok = ref(tok, pos)[:, -1].argmax(-1, keepdim=True)
+        pos += 1
+    torch.cuda.synchronize(dev)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tok = ref(tok, pos)[:, -1].argmax(-1, keepdim=True)
+        pos += 1
+    torch.cuda.synchronize(dev)
+    sec = time.perf_counter() - t0
+    from spec_mcts_b200 import kernels as K
+    del ref
+    K.relayout_cache_config(clear=True)
+    return {"what": "the reference's hf_model_q40_kv_shared.Transformer, unmodified, on this repository's "
+                    "triton_kernels module (wall clock, its own Python loop), width 1",
+            "tokens_per_s": steps / sec, "ms_per_step": sec / steps * 1e3}
+
+
 def gemv_roofline(model, width, reps):
     """The dominant kernel alone: every Q4_0 matmul of the model in layer order (3.4 GB of
     distinct weights per pass, so nothing is served from L2), launched exactly as a decode step
@@ -312,23 +411,15 @@ def gemv_roofline(model, width, reps):
     return total_bytes / sec / 1e9, sec / launches, total_bytes / launches, name
 
 
-def run_70b_tp(args):
-    """`--workload 70b-tp` (launch with torchrun, one rank per GPU): CodeLlama-70B-architecture
-    Q4_0 decode, 80 layers, hidden 8192, 64 query / 8 kv heads, FFN 28672, vocab 32016, random
-    shards per rank, prompt cache of 1024 tokens, 64 branches; tensor parallel over all ranks
-    with an NCCL all-reduce after wo and w2.  Prints its own JSON line on rank 0."""
+def measure_70b_tp(world, rank, dev, steps, warmup, n_layers=80, branches=64, hbm_peak=6650.0):
+    """CodeLlama-70B-architecture Q4_0 decode (80 layers, hidden 8192, 64 query / 8 kv heads, FFN 28672,
+    vocab 32016, random shards per rank, prompt cache of 1024 tokens, 64 branches) tensor parallel over
+    the ranks of the default process group, all-reduce after wo and w2.  Returns the result dict on rank 0."""
     import torch
     import torch.distributed as dist
     from spec_mcts_b200.model import ModelArgs, Transformer, random_init_
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    B, P, steps, warmup = args.tp_branches, 1024, args.steps, max(args.warmup, 3)
-    margs = ModelArgs(dim=8192, n_layers=args.tp_layers, n_heads=64, n_kv_heads=8, vocab_size=VOCAB, multiple_of=4096,
+    B, P = branches, 1024
+    margs = ModelArgs(dim=8192, n_layers=n_layers, n_heads=64, n_kv_heads=8, vocab_size=VOCAB, multiple_of=4096,
                       ffn_dim_multiplier=1.3, max_batch_size=B, max_seq_len=max(steps + warmup + 2, 72),
                       max_prompt_seq_len=P)
     with torch.inference_mode():
@@ -354,26 +445,171 @@ def run_70b_tp(args):
         e1.record()
         torch.cuda.synchronize(dev)
         sec = e0.elapsed_time(e1) * 1e-3
+        # the step's collectives alone: the same 2 * n_layers all-reduces of [B, 8192] fp16, from a graph
+        ar_ms = None
         if world > 1:
-            t = torch.tensor([sec], device=dev, dtype=torch.float64)
+            buf = torch.zeros((B, 8192), dtype=torch.float16, device=dev)
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                dist.all_reduce(buf)
+            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.synchronize(dev)
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                for _ in range(2 * n_layers):
+                    dist.all_reduce(buf)
+            for _ in range(2):
+                gr.replay()
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(4):
+                gr.replay()
+            a1.record()
+            torch.cuda.synchronize(dev)
+            t = torch.tensor([sec, a0.elapsed_time(a1) * 1e-3 / 4], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            sec = float(t.item())
-    if rank == 0:
+            sec, ar_ms = float(t[0].item()), float(t[1].item()) * 1e3
+            del gr
+        model.release_graphs()
         hid = model.layers[0].feed_forward.full_hidden_dim
-        per_layer = (8192 * 8192 * 2 + 2 * 8192 * 1024 + 3 * 8192 * hid)
-        wbytes = margs.n_layers * (per_layer // 2 + per_layer // 64 * 2) / world + VOCAB * 8192 * 2
-        print(json.dumps({"workload": "codellama-70b-arch q4_0 decode, tensor parallel", "n_gpus": world,
-                          "layers": margs.n_layers, "branches": B, "prompt_len": P, "steps": steps,
-                          "ms_per_step": sec / steps * 1e3, "tokens_per_s": B * steps / sec,
-                          "weight_bytes_per_gpu_per_step": wbytes,
-                          "weight_stream_gbs_per_gpu": wbytes / (sec / steps) / 1e9,
-                          "allreduces_per_step": 2 * margs.n_layers, "allreduce_bytes": B * 8192 * 2}), flush=True)
-    if world > 1:
-        # captured graphs hold NCCL work; tearing the process group down under them can block, and
-        # there is nothing left to save: synchronise and leave
-        torch.cuda.synchronize(dev)
+    per_layer = (8192 * 8192 * 2 + 2 * 8192 * 1024 + 3 * 8192 * hid)
+    wbytes = margs.n_layers * (per_layer // 2 + per_layer // 64 * 2) / world + VOCAB * 8192 * 2
+    del model
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    gbs = wbytes / (sec / steps) / 1e9
+    return {"workload": "codellama-70b-arch q4_0 decode, tensor parallel", "n_gpus": world, "layers": margs.n_layers,
+            "branches": B, "prompt_len": P, "steps": steps, "warmup": warmup, "ms_per_step": sec / steps * 1e3,
+            "tokens_per_s": B * steps / sec, "weight_bytes_per_gpu_per_step": wbytes,
+            "weight_stream_gbs_per_gpu": gbs, "frac_of_hbm_peak_per_gpu": gbs / hbm_peak,
+            "allreduces_per_step": 2 * margs.n_layers, "allreduce_bytes": B * 8192 * 2,
+            "allreduce_ms_per_step_alone": ar_ms}
+
+
+def finish_distributed(dev):
+    """Leave a multi-rank run.  Captured CUDA graphs that contain NCCL collectives keep the communicator's
+    work queue referenced, and tearing the communicator down while such a graph is alive waits for
+    it; the models release their graphs first (Transformer.release_graphs), then the group is destroyed.
+    A watchdog ends the process if the teardown still does not return: the result line is already out."""
+    import torch
+    import torch.distributed as dist
+    torch.cuda.synchronize(dev)
+    sys.stdout.flush()
+    threading.Timer(20.0, lambda: os._exit(0)).start()
+    try:
+        dist.destroy_process_group()
+    finally:
         sys.stdout.flush()
         os._exit(0)
+
+
+def run_70b_tp(args):
+    """`--workload 70b-tp` (launch with torchrun, one rank per GPU): the tensor-parallel 70B decode alone;
+    prints its own JSON line on rank 0."""
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    res = measure_70b_tp(world, rank, dev, args.steps, max(args.warmup, 3), args.tp_layers, args.tp_branches)
+    if rank == 0:
+        print(json.dumps(res), flush=True)
+    if world > 1:
+        finish_distributed(dev)
+
+
+def kernel_configs(dev, hbm):
+    """The kernel-level configurations in short form: (1) the isolated 4096 x 4096 Q4_0 GEMV at batch 1 — 32
+    distinct weight matrices per timed pass (285 MB, larger than L2), through the drop-in `matmul_q40` and
+    through the decode step's tiled launch; (3) shared-prefix tree attention, 2048 shared keys, 64 branches
+    with 0..256 private tokens in 16-token pages."""
+    import numpy as np
+    import torch
+    from spec_mcts_b200 import kernels as K
+    g = torch.Generator(device=dev).manual_seed(0)
+    N = Kd = 4096
+    NW = 32
+    ws = []
+    for _ in range(NW):
+        w = (torch.randn((Kd, N), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.float16)
+        ws.append(K.quantize_q40(w, 64))
+    tiled = [K.relayout_tiled(q, sc, (Kd, N)) for q, sc in ws]
+    a = torch.randn((1, Kd), generator=g, device=dev, dtype=torch.float16)
+
+    def timed(fn, reps=20):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize(dev)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            fn()
+        for _ in range(3):
+            gr.replay()
+        torch.cuda.synchronize(dev)
+        ts = []
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            gr.replay()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            ts.append(e0.elapsed_time(e1) * 1e-3)
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    byts = N * Kd * (0.5 + 2 / 64) + 2 * Kd + 2 * N
+    out = {}
+    for name, fn in (("matmul_q40", lambda: [K.matmul_q40(a, q, sc, (Kd, N)) for q, sc in ws]),
+                     ("tiled_launch", lambda: [K.gemv_fused(0, a, [(t, None, (Kd, N))], tiled=True, use_pdl=True)
+                                               for t in tiled])):
+        sec = timed(fn) / NW
+        out["gemv_4096x4096_m1_" + name] = {"us": sec * 1e6, "algorithmic_bytes": byts, "GBs": byts / sec / 1e9,
+                                            "frac_of_measured_hbm": byts / sec / 1e9 / hbm,
+                                            "frac_of_8000_gbs": byts / sec / 1e9 / 8000.0}
+    del ws, tiled
+    K.relayout_cache_config(clear=True)
+    H, D, P0, B, page = 32, 128, 2048, 64, 16
+    rng = np.random.default_rng(0)
+    lens = rng.integers(0, 257, size=B)
+    npages = [(int(l) + page - 1) // page for l in lens]
+    tbl = np.zeros((B, max(max(npages), 1)), dtype=np.int32)
+    nxt = 0
+    for b in range(B):
+        for j in range(npages[b]):
+            tbl[b, j] = nxt
+            nxt += 1
+    tot = max(nxt, 1)
+    pk = torch.randn((P0, H, D), generator=g, device=dev, dtype=torch.float16)
+    pv = torch.randn((P0, H, D), generator=g, device=dev, dtype=torch.float16)
+    kpool = torch.randn((H, tot * page, D), generator=g, device=dev, dtype=torch.float16)
+    vpool = torch.randn((H, tot * page, D), generator=g, device=dev, dtype=torch.float16)
+    qq = torch.randn((B, H, D), generator=g, device=dev, dtype=torch.float16)
+    tbl_d, lens_d = torch.from_numpy(tbl).to(dev), torch.from_numpy(lens.astype(np.int32)).to(dev)
+    sec = timed(lambda: K.shared_prefix_attn(qq, pk, pv, P0, tbl_d, lens_d, kpool, vpool, page_size=page))
+    prefix_bytes = 2 * P0 * H * D * 2
+    suffix_bytes = int(lens.sum()) * H * D * 2 * 2
+    alg = prefix_bytes + suffix_bytes + 2 * B * H * D * 2
+    naive = B * prefix_bytes + suffix_bytes
+    out["tree_attention_prefix2048_b64"] = {"us": sec * 1e6, "algorithmic_bytes": alg, "GBs": alg / sec / 1e9,
+                                            "frac_of_measured_hbm": alg / sec / 1e9 / hbm,
+                                            "kv_bytes_if_prefix_were_read_per_branch": naive,
+                                            "effective_kv_GBs": naive / sec / 1e9,
+                                            "effective_kv_over_measured_hbm": naive / sec / 1e9 / hbm}
+    return out
 
 
 def run_kernel_sweep(args):
@@ -499,6 +735,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--widths", default=",".join(str(w) for w in WIDTHS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="only the headline measurement: no kernel-level configurations, no second decode path, "
+                         "no reference class on the drop-in kernels, no 70B tensor-parallel run")
     ap.add_argument("--skip-prefill", action="store_true",
                     help="profiling aid: fill the prompt cache with random K/V instead of running the prompt "
                          "(keeps a profiler capture short); not a valid benchmark configuration")
@@ -567,13 +806,14 @@ def main():
             torch.cuda.synchronize(dev)
 
         sampler = ClockSampler(local_rank)
-        results, e2e_res = {}, {}
+        results, e2e_res, launches = {}, {}, {}
         barrier()
         if rank == 0:
             sampler.start()
         for w in widths:
             barrier()
             sec = timed_decode(model, w, steps, warmup, PROMPT_LEN)
+            launches[w] = model.launches_per_step
             barrier()
             if world > 1:
                 t = torch.tensor([sec], device=dev, dtype=torch.float64)
@@ -590,6 +830,30 @@ def main():
                 sec = float(t.item())
             e2e_res[w] = (sec, h2d, d2h)
         roof = gemv_roofline(model, widths[0], reps=5) if rank == 0 else None
+        by_path = None
+        if rank == 0 and world == 1 and not args.no_extras:
+            # the same step with the kernels that keep the reference's operand rounding, fp16(code * scale)
+            model.use_tiled = False
+            sec_ref = timed_decode(model, widths[0], min(steps, 32), warmup, PROMPT_LEN)
+            model.use_tiled = True
+            by_path = {"tiled (default)": {"ms_per_step": results[widths[0]] / steps * 1e3},
+                       "checkpoint layout, reference operand rounding": {"ms_per_step": sec_ref / min(steps, 32) * 1e3}}
+        drop_in = reference_class_on_drop_in(model, dev) if rank == 0 and world == 1 and not args.no_extras else None
+        model.release_graphs()
+
+    kernels = None
+    if rank == 0 and world == 1 and not args.no_extras:
+        del model
+        torch.cuda.empty_cache()
+        with torch.inference_mode():
+            kernels = kernel_configs(dev, hbm_peak)
+    tp = None
+    if world > 1 and not args.no_extras:
+        # the geometry that shards: 70B tensor parallel on the same ranks, after the replicas
+        del model
+        torch.cuda.empty_cache()
+        dist.barrier()
+        tp = measure_70b_tp(world, rank, dev, 16, 3, args.tp_layers, args.tp_branches, hbm_peak)
 
     if rank == 0:
         w0 = widths[0]
@@ -601,11 +865,7 @@ def main():
             "metric": METRIC, "value": tok_s[w0], "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
             "ms_per_step": results[w0] / steps * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": "codellama-7b-arch q4_0 decode (32 layers, hidden 4096, ffn 11008, vocab 32016), "
-                                   "random-init N(0,0.02^2) weights, prompt 512 shared, greedy, width %d" % w0,
-                       "group": 64, "prompt_len": PROMPT_LEN, "widths": widths, "replicas": world,
-                       "skip_prefill": bool(args.skip_prefill),
-                       "l2": "inputs larger than L2 (3.7 GB of weights streamed per step)"},
+            "config": workload_config(widths, world, args.skip_prefill),
             "by_width": {str(w): {"tokens_per_s": tok_s[w], "ms_per_step": results[w] / steps * 1e3,
                                   "e2e_tokens_per_s": e2e_tok_s[w]} for w in widths},
             "step_weight_stream": {"bytes_per_step": step_bytes,
@@ -614,15 +874,22 @@ def main():
             "roofline": {"bound": "hbm", "kernel": roof_kernel, "achieved": ach, "peak": hbm_peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": ach / hbm_peak,
                          "avg_launch_us": sec_per_launch * 1e6, "alg_bytes_per_launch": bytes_per_launch,
-                         # dram read+write bytes per average launch from the ncu capture summarised in
-                         # profiles/gemv_tiled_kernel_7b_shapes_ncu.md (traffic == algorithmic bytes)
-                         "traffic": TILED_TRAFFIC_PER_LAUNCH if roof_kernel.startswith("gemv_tiled") else None},
+                         "traffic": measured_traffic(roof_kernel.split("<")[0])},
             "e2e": {"value": e2e_tok_s[w0], "unit": UNIT, "h2d_bytes_per_step": e2e_res[w0][1],
                     "d2h_bytes_per_step": e2e_res[w0][2]},
             "prefill_ms": prefill_ms,      # prompt pass of PROMPT_LEN tokens (not part of the decode metric)
-            "gpu_launches": steps * model.launches_per_step,
+            # this library's kernels enqueued inside the timed region of the headline width
+            "gpu_launches": steps * launches[w0],
             "clocks": clocks,
         }
+        if by_path is not None:
+            line["by_path"] = by_path
+        if drop_in is not None:
+            line["drop_in"] = drop_in
+        if kernels is not None:
+            line["kernels"] = kernels
+        if tp is not None:
+            line["tp_70b"] = tp
         if not args.no_cpu and world == 1:
             threads = os.cpu_count() or 1
             t_layer, td, tm = cpu_layer_sample(1, threads, 5)
@@ -634,11 +901,7 @@ def main():
             line["cpu_baseline"] = None
         print(json.dumps(line), flush=True)
     if world > 1:
-        # captured graphs hold NCCL work; tearing the process group down under them can block, and
-        # there is nothing left to save: synchronise and leave
-        torch.cuda.synchronize(dev)
-        sys.stdout.flush()
-        os._exit(0)
+        finish_distributed(dev)
 
 
 if __name__ == "__main__":

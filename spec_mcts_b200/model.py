@@ -250,6 +250,13 @@ class Transformer(nn.Module):
             layer.attention.cache_prompt_len = 0
         self._prefix_len_dev.zero_()
 
+    def release_graphs(self):
+        """Destroy the captured decode graphs (they are rebuilt on the next step).  With tensor parallelism
+        the graphs contain NCCL collectives, and a communicator cannot be torn down while a graph that
+        captured its work is alive: call this before torch.distributed.destroy_process_group()."""
+        torch.cuda.synchronize(self.device)
+        self._graphs.clear()
+
     # ------------------------------------------------------------------ prompt
     def _prefill(self, tokens):
         p = self.params

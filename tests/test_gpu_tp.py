@@ -92,8 +92,13 @@ def _worker(rank, world, port, ret):
             toks, pos = nxt, pos + 1
         if rank == 0:
             ret["errs"] = errs
-    # the captured graphs hold NCCL work; tearing the group down under them can block
-    torch.cuda.synchronize()
+        # graphs that captured NCCL collectives must be gone before the communicator is torn down
+        tpm.release_graphs()
+        if ref is not None:
+            ref.release_graphs()
+    import threading
+    threading.Timer(20.0, lambda: os._exit(0)).start()      # never block the test run on a teardown
+    dist.destroy_process_group()
     os._exit(0)
 
 
