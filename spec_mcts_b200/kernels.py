@@ -182,8 +182,13 @@ def matmul_q40(a: torch.Tensor, b_w: torch.Tensor, b_s: torch.Tensor, b_shape, *
         return c
     small = M <= 16 and group_size == 64 and K % 16 == 0 and K >= 64 and a.data_ptr() % 16 == 0 and c.stride(1) == 1
     if small and N % 256 == 0 and (relayout if relayout is not None else _relayout_cfg["enabled"]):
+        n_before = len(_relayout_cache)
         tiled = _tiled_copy_of(b_w, b_s, K, N)
-        if tiled is not None and (_tiled_gemv(dev, a, tiled, c, M, N, K) or _stream_gemv(dev, a, tiled, c, M, N, K)):
+        # programmatic launch (weights requested while the previous kernel drains) except right after the
+        # kernel that wrote the copy
+        pdl = len(_relayout_cache) == n_before
+        if tiled is not None and (_tiled_gemv(dev, a, tiled, c, M, N, K, pdl) or
+                                  _stream_gemv(dev, a, tiled, c, M, N, K)):
             return c
     if small and N % 128 == 0 and _cluster_gemv(dev, a, b_w, b_s, c, M, N, K):
         return c
@@ -255,15 +260,15 @@ def _tiled_copy_of(b_w, b_s, K, N):
     return copy
 
 
-def _tiled_gemv(dev, a, tiled, c, M, N, K) -> bool:
+def _tiled_gemv(dev, a, tiled, c, M, N, K, pdl=False) -> bool:
     """Mode 0 of q40_gemv_tiled (cluster split-K) on a tiled copy; False if this device cannot schedule
     the clusters."""
     import ctypes
     P = ctypes.c_void_p * 1
     for cluster in ((_cluster_size.get(dev.index, 16),) if dev.index in _cluster_size else (16, 8)):
         rc = lib.q40_gemv_tiled(0, 1, P(tiled.data_ptr()), P(0), P(c.data_ptr()), (ctypes.c_int * 1)(N), c.stride(0),
-                                a.data_ptr(), a.stride(0), M, K, None, None, 0, 0.0, None, 0, None, 0, cluster, 0,
-                                _stream(dev))
+                                a.data_ptr(), a.stride(0), M, K, None, None, 0, 0.0, None, 0, None, 0, cluster,
+                                1 if pdl else 0, _stream(dev))
         if rc == 0:
             _cluster_size[dev.index] = cluster
             return True

@@ -216,10 +216,13 @@ def test_matmul_7b_shapes_linearity_and_repeatability(K):
         c100 = K.matmul_q40(x, q, s, (Kd, N))
         assert torch.equal(c100, K.matmul_q40(x, q, s, (Kd, N)))
         c1 = K.matmul_q40(x[37:38].contiguous(), q, s, (Kd, N))
+        c8 = K.matmul_q40(x[30:38].contiguous(), q, s, (Kd, N))
         c10 = K.matmul_q40(x[30:40].contiguous(), q, s, (Kd, N))
-        # rows do not depend on their batch within a kernel family (M <= 16: split-K GEMV); the
-        # tensor-core kernel used above 16 rows sums in a different order, so it is compared closely
-        assert torch.equal(c1[0], c10[7])
+        # rows do not depend on their batch within a kernel variant (up to 8 rows: one MMA batch tile per
+        # warp); 9..16 rows split k differently over the warps and the tensor-core kernel used above 16
+        # rows sums in yet another order, so those are compared closely
+        assert torch.equal(c1[0], c8[7])
+        assert_close(host(c10[7:8]), host(c1), rtol=1e-2, atol=2e-3)
         assert_close(host(c100[37:38]), host(c1), rtol=1e-2, atol=2e-3)
         ref = (x[:4].float() @ deq.float()).to(torch.float16)
         assert_close(host(c100[:4]), host(ref))
