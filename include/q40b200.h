@@ -198,6 +198,20 @@ int q40_gemv_stream(int mode, int nmat, const void* const* bw_tiled, void* const
                     int smem_budget, int use_pdl, void* stream);
 int q40_gemv_stream_ss_count(int N);
 
+/* Tail of a decode step in one launch: logits[M, V] = fp16(RMSNorm(h; norm_w, eps) @ w^T) for the fp16
+ * lm_head w [V, K] (row-major), 1 <= M <= 16, K % 128 == 0.  ss_in [M, ss_count] are partial sums of
+ * squares of the rows of h as a mode-2 matmul launch leaves them (NULL: computed here).  If tok_out is
+ * given, the arg-max of every row of the fp16 logits (ties: the smaller index) is written to tok_out[m]
+ * (int64) and pos[m] (int32, may be NULL) is advanced by one — greedy decoding without the host.
+ * `scratch`: q40_lm_head_scratch_bytes() bytes, 8-byte aligned, zero-filled once (left zeroed);
+ * required with tok_out.
+ * Replaces: self.norm + self.output of Transformer.forward (hf_model_q40_kv_shared.py:508-510) and the
+ * arg-max a greedy harness applies to its result. */
+int q40_lm_head(const void* h, int64_t ldh, const float* ss_in, int ss_count, const void* norm_w, float eps,
+                const void* w, int V, int K, void* logits, int64_t ldl, int M, int64_t* tok_out,
+                int32_t* pos, void* scratch, int use_pdl, void* stream);
+size_t q40_lm_head_scratch_bytes(void);
+
 /* ---- decode attention (one query token per branch) ---------------------------------- */
 
 /* q[B,H,D], k/v[B,Hkv,L,D] contiguous fp16 -> o[B,H,D]; scale 1/sqrt(D); D == 128;

@@ -67,6 +67,9 @@ SIGNATURES = {
                                 c_void_p, c_void_p, c_int, c_float, c_void_p, c_int64, c_void_p, c_int, c_void_p,
                                 c_size_t, c_int, c_int, c_void_p]),
     "q40_gemv_stream_ss_count": (c_int, [c_int]),
+    "q40_lm_head": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p,
+                            c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "q40_lm_head_scratch_bytes": (c_size_t, []),
     "q40_attn_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p]),
     "q40_attn_paged": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,

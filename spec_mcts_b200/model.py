@@ -220,6 +220,9 @@ class Transformer(nn.Module):
         # width <= 16: rotary embedding, cache append and attention as one cluster launch
         # single-launch attention (rotary + append + attention) up to this width; wider steps read the
         # shared prompt once for all branches with the three-launch path
+        # width <= 8: final RMSNorm, fp16 lm_head, arg-max and position bump as one launch (above, the
+        # library GEMM is faster than the streaming kernel)
+        self.use_fused_tail = True
         self.use_fused_attn = True
         self.fused_attn_max_width = 1
         # ... and while prompt + suffix fit in two register batches of its clusters (640 keys each);
@@ -489,6 +492,18 @@ class Transformer(nn.Module):
             self._fused(1, [lin], [bufs["logits_pad"]], vp, h, p.dim, B, norm_w=self.norm.weight, ss_in=ss_ffn,
                         ss_in_count=c_ffn, st=st, bufs=bufs)
             logits = bufs["logits_pad"][:, :p.vocab_size]
+        elif self.use_fused_tail and p.dim % 128 == 0 and B <= 8:
+            # final RMSNorm + fp16 lm_head + (greedy feedback) arg-max and position bump: one launch
+            logits = bufs["logits"]
+            if "lm_scratch" not in bufs:
+                bufs["lm_scratch"] = torch.zeros(lib.q40_lm_head_scratch_bytes(), dtype=torch.uint8, device=self.device)
+            fb = self.greedy_feedback
+            check(lib.q40_lm_head(h.data_ptr(), p.dim, ss_ffn.data_ptr(), c_ffn, self.norm.weight.data_ptr(),
+                                  float(p.norm_eps), self.output.weight.data_ptr(), p.vocab_size, p.dim,
+                                  logits.data_ptr(), logits.stride(0), B,
+                                  self._tok_dev.data_ptr() if fb else None, self._pos_dev.data_ptr() if fb else None,
+                                  bufs["lm_scratch"].data_ptr(), 1 if self.use_pdl else 0, st), "q40_lm_head")
+            return logits
         else:
             self._norm(h, None, self.norm.weight, bufs["xn"], st)
             logits = bufs["logits"]
@@ -597,7 +612,8 @@ class Transformer(nn.Module):
         if not self.use_cuda_graph:
             return self._decode_body(B)
         key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster, self.use_stream,
-               self.use_tiled, self.use_fused_attn, self.fused_attn_max_width, self.stream_smem_budget)
+               self.use_tiled, self.use_fused_attn, self.fused_attn_max_width, self.stream_smem_budget,
+               self.use_fused_tail)
         g = self._graphs.get(key)
         if g is None:
             # torch requires capture on a side stream after a warm-up run; with greedy feedback that run
@@ -614,7 +630,8 @@ class Transformer(nn.Module):
                     # this device cannot schedule 16-CTA clusters: use the portable size
                     self.max_cluster = 8
                     key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster, self.use_stream,
-                           self.use_tiled, self.use_fused_attn, self.fused_attn_max_width, self.stream_smem_budget)
+                           self.use_tiled, self.use_fused_attn, self.fused_attn_max_width, self.stream_smem_budget,
+                           self.use_fused_tail)
                     self._decode_body(B)
             torch.cuda.current_stream(self.device).wait_stream(s)
             torch.cuda.synchronize(self.device)

@@ -232,8 +232,9 @@ def test_q4_lm_head_option(small):
         # same position again: the cache row is rewritten with the same values
         got = model(toks, pos)[:, -1].float()
         lin = model._lm_head_q4
-        xn = model._step_buffers(3)["xn"]                           # written by the fp16-head step above
-        want = KK.matmul_q40(xn[:3].contiguous(), lin.w, lin.s, lin.kn())[:, :got.shape[-1]].float()
+        # the residual stream of the step is left in the step's buffer; its final RMSNorm feeds both heads
+        xn = KK.rmsnorm(model._step_buffers(3)["h"][:3].clone(), model.norm.weight, model.params.norm_eps)
+        want = KK.matmul_q40(xn.contiguous(), lin.w, lin.s, lin.kn())[:, :got.shape[-1]].float()
     np.testing.assert_allclose(got.cpu().numpy(), want.cpu().numpy(), rtol=2e-2, atol=2e-2)
     # and it is a quantised version of the fp16 head, not something else
     rel = float((got - ref).norm() / ref.norm())
