@@ -212,6 +212,43 @@ int q40_lm_head(const void* h, int64_t ldh, const float* ss_in, int ss_count, co
                 int32_t* pos, void* scratch, int use_pdl, void* stream);
 size_t q40_lm_head_scratch_bytes(void);
 
+/* ---- token tree search: one sampling step on the device ----------------------------------- */
+
+/* For each of B live branches: scaled logits (temp > 0: fp16(logit / temp), as the reference's
+ * fp16 tensor / python float; temp <= 0: logit / (slope * (counts[b] - 1) + 0.1) in fp32, the
+ * reference's per-branch temperature by particle count, slope = (|temp| - 0.1) / (batch - 1)), the
+ * top_k (<= 32) candidates ordered by (value descending, token id ascending), their softmax (rounded to
+ * fp16 when temp > 0), counts[b] draws with replacement — draws[b, i] in [0, 1) selects the first
+ * candidate whose running fp32 probability sum exceeds draws[b, i] times the total — and the distinct
+ * sampled tokens in ascending order with their multiplicities: n_unique[b], uni_tok[b, 0..], uni_cnt[b, 0..]
+ * (rows of 32).  probs_out / cand_out (rows of 32, may be NULL) receive the candidate list.
+ * Replaces: mcts.search's per-branch temperature / torch.topk / F.softmax / torch.multinomial /
+ * torch.unique sequence (mcts.py:110-131). */
+int q40_tree_sample(const void* logits, int64_t ld, int B, int V, int top_k, float temp, float slope,
+                    const int32_t* counts, const float* draws, int64_t draws_ld, int32_t* n_unique,
+                    int32_t* uni_tok, int32_t* uni_cnt, float* probs_out, int32_t* cand_out, void* stream);
+
+/* Branch bookkeeping of token `step` for the *curr live branches, in branch order: the first distinct
+ * token stays on its branch, each further one creates a branch while fewer than `batch` exist (token
+ * history copied from the origin, counts and last token set, fork_src[new] = origin); then, for all
+ * `batch` rows, tokens of finished rows are zeroed, the terminal-sequence matcher and the end-of-
+ * sequence test run, lengths and the alive mask are updated, batch_stats[step] = live branches and
+ * *all_done = (finished rows == live branches).  *n_forks / *fork_base describe the branches created.
+ * Replaces: mcts.search's fork / bookkeeping block and detectTerminal (mcts.py:133-176, 14-28). */
+int q40_tree_fork(const int32_t* n_unique, const int32_t* uni_tok, const int32_t* uni_cnt, int64_t* results,
+                  int max_new, int step, int batch, int32_t* counts, int32_t* last_tok, uint8_t* alive,
+                  int32_t* results_len, int32_t* end_state, const int64_t* term_seq, int term_len,
+                  int64_t eos, int32_t* curr, int32_t* fork_src, int32_t* n_forks, int32_t* fork_base,
+                  uint8_t* batch_stats, int32_t* all_done, void* stream);
+
+/* For the *n_forks branches created by q40_tree_fork: copy copy_bytes (a multiple of 16) of branch
+ * fork_src[b] to branch b in every layer of a cache tensor [n_layers, branches, ...] with the given
+ * byte strides.  max_forks bounds the grid (the count itself stays on the device).
+ * Replaces: Attention.fork / Transformer.fork (hf_model_q40_kv_shared.py:282-297, 512-516). */
+int q40_tree_fork_copy(void* cache, int64_t layer_stride, int64_t branch_stride, int64_t copy_bytes, int n_layers,
+                       const int32_t* fork_src, const int32_t* n_forks, const int32_t* fork_base, int max_forks,
+                       void* stream);
+
 /* ---- decode attention (one query token per branch) ---------------------------------- */
 
 /* q[B,H,D], k/v[B,Hkv,L,D] contiguous fp16 -> o[B,H,D]; scale 1/sqrt(D); D == 128;

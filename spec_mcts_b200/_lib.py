@@ -70,6 +70,13 @@ SIGNATURES = {
     "q40_lm_head": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p,
                             c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "q40_lm_head_scratch_bytes": (c_size_t, []),
+    "q40_tree_sample": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_int64,
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "q40_tree_fork": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                              c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_void_p, c_void_p, c_void_p]),
+    "q40_tree_fork_copy": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                   c_void_p]),
     "q40_attn_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p]),
     "q40_attn_paged": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,

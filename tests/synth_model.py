@@ -98,3 +98,30 @@ def load_synthetic(model, quantize, base_seed, dim, n_heads, n_kv_heads, hidden,
                 h.update(s.cpu().numpy().tobytes())
             del wt
     return h.hexdigest()
+
+
+# ---------------------------------------------------------------------------------------------
+# synthetic logits for the tree-search tests
+# ---------------------------------------------------------------------------------------------
+TREE_TERMINAL_SEQ = (29961, 29914, 20055, 4690, 1164, 29962)      # the reference's TERMINAL_SEQ (mcts.py:12)
+
+
+def tree_logits(seed, call, nrows, vocab, forced=None):
+    """fp16 logits [nrows, vocab] of the `call`-th model call of a synthetic tree search (numpy).  Every
+    row holds the same 64 well-separated top values (9.0, 8.9, ...: no two candidates tie, whatever the
+    temperature) on token ids drawn by a per-(seed, call, row) permutation, the rest uniform in
+    [-5, 2.5).  `forced` maps (call, row) -> token id that gets the value 20 (sampled almost surely):
+    used to drive rows into the end-of-sequence token and through the terminal sequence."""
+    import numpy as np
+    out = np.empty((nrows, vocab), dtype=np.float16)
+    top = (9.0 - 0.1 * np.arange(64)).astype(np.float16)
+    for r in range(nrows):
+        rng = np.random.default_rng([seed, call, r])
+        vals = rng.uniform(-5.0, 2.5, size=vocab).astype(np.float16)
+        vals[:64] = top
+        row = np.empty(vocab, dtype=np.float16)
+        row[rng.permutation(vocab)] = vals
+        if forced and (call, r) in forced:
+            row[forced[(call, r)]] = np.float16(20.0)
+        out[r] = row
+    return out

@@ -1,10 +1,13 @@
 """Pins the numpy oracle to vectors generated from the reference's own torch functions."""
 import hashlib
+import os
 
 import numpy as np
 import pytest
 
 from oracle import q40_oracle as O
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 QCASES = ["w_normal", "w_unit", "w_uniform_pos", "w_edges"]
 
@@ -160,3 +163,38 @@ def test_model_oracle():
         pos += 1
     rels = np.array(rels)
     assert rels.max() < 1e-1 and np.median(rels) < 5e-3
+
+
+def test_tree_oracle():
+    """oracle/tree_oracle.py against the reference's own mcts.search loop (tests/golden/make_golden_tree.py):
+    same tokens, lengths, live-branch counts and fork calls for all four stored searches."""
+    import sys
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import synth_model as SM
+    from oracle import tree_oracle as T
+    G = np.load(os.path.join(ROOT, "tests", "golden", "tree_search.npz"))
+    for name in sorted({k.split(".")[0] for k in G.files}):
+        batch, max_new, seed = (int(v) for v in G[name + ".config"])
+        temp = float(G[name + ".temp"])
+        forced = {(int(c), int(r)): int(t) for c, r, t in G[name + ".forced"]}
+        draws = G[name + ".draws"]
+        st = T.TreeState(batch, max_new, SM.TREE_TERMINAL_SEQ, eos=2)
+        forks, steps = [], max_new
+        for t in range(max_new):
+            curr0 = st.curr
+            lg = SM.tree_logits(seed, t, curr0, 32016, forced)
+            made, stop = st.step(t, lg, temp, draws[t])
+            # the reference issues one fork call per origin: (model call, origin, first new branch, count)
+            by_origin = {}
+            for o, nb in made:
+                by_origin.setdefault(o, []).append(nb)
+            forks += [(t, o, nbs[0], len(nbs)) for o, nbs in by_origin.items()]
+            if stop:
+                steps = t + 1
+                break
+        ref = G[name + ".results"]
+        assert ref.shape == (st.curr, steps), name
+        np.testing.assert_array_equal(st.results[:st.curr, :steps], ref)
+        np.testing.assert_array_equal(st.results_len, G[name + ".results_len"])
+        np.testing.assert_array_equal(st.batch_stats[:steps], G[name + ".batch_stats"][:steps])
+        np.testing.assert_array_equal(np.array(forks, dtype=np.int64).reshape(-1, 4), G[name + ".forks"])
