@@ -46,6 +46,8 @@ SIGNATURES = {
                                c_void_p, c_void_p]),
     "q40_gemm_kn_tc_multi": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_int, c_int, c_void_p, c_int, c_void_p]),
+    "q40_gemm_tiled_tc_multi": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_int, c_int, c_void_p, c_int, c_void_p]),
     "q40_gemm_kn_static": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
                                    c_int, c_int, c_void_p]),
     "q40_gemm_kn_static_max_workspace": (c_size_t, []),

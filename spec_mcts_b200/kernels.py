@@ -401,6 +401,33 @@ def gemv_fused(mode: int, a: torch.Tensor, weights, *, norm_w=None, ss_in=None, 
     return outs
 
 
+def gemm_tiled_tc(a: torch.Tensor, weights, use_pdl: bool = False):
+    """[a @ deq(B_i)] for 1-3 (tiled copy, (K, N)) pairs sharing the activations a [M > 16, K] on the tensor
+    cores (q40_gemm_tiled_tc_multi in include/q40b200.h); the outputs are column slices of one buffer.
+    Raises if a bounded wait inside the kernel expired."""
+    import ctypes
+    dev = _need_cuda(a, *[w[0] for w in weights])
+    M, K = a.shape
+    n = len(weights)
+    Ns = [int(w[1][1]) for w in weights]
+    for w in weights:
+        assert int(w[1][0]) == K
+    buf = torch.empty((M, sum(Ns)), dtype=torch.float16, device=dev)
+    outs, c0 = [], 0
+    for N in Ns:
+        outs.append(buf[:, c0:c0 + N])
+        c0 += N
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    P = ctypes.c_void_p * n
+    check(lib.q40_gemm_tiled_tc_multi(n, a.data_ptr(), a.stride(0), P(*[w[0].data_ptr() for w in weights]),
+                                      P(*[o.data_ptr() for o in outs]), (ctypes.c_int64 * n)(*[buf.stride(0)] * n),
+                                      (ctypes.c_int * n)(*Ns), M, K, err.data_ptr(), 1 if use_pdl else 0,
+                                      _stream(dev)), "q40_gemm_tiled_tc_multi")
+    if int(err.item()) != 0:
+        raise Q40Error("gemm_tiled_tc: a bounded wait inside the kernel expired")
+    return outs
+
+
 def gemv_stream(mode: int, a: torch.Tensor, weights, *, norm_w=None, ss_in=None, eps: float = 1e-5, h_in=None,
                 use_pdl: bool = False, smem_budget: int = 0, workspace: Optional[torch.Tensor] = None):
     """gemv_fused on the byte-balanced stream-K launch (q40_gemv_stream in include/q40b200.h).

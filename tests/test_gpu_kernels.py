@@ -489,3 +489,39 @@ def test_attn_tree_fused_matches_two_call_path(K, plen, maxP, use_pdl):
         assert torch.equal(ks1.view(torch.int16), ks2.view(torch.int16))
         assert torch.equal(vs1.view(torch.int16), vs2.view(torch.int16))
         assert_close(host(o2), host(o1), rtol=1e-2, atol=2e-3)
+
+
+@pytest.mark.parametrize("M", [17, 64, 100, 128, 200, 256, 300])
+def test_matmul_tiled_tc_matches_oracle(K, M):
+    """The tensor-core matmul on tiled weight copies: three matrices sharing the activations (k split over a
+    cluster at these sizes), against the numpy oracle; also bit-equal to the checkpoint-layout tensor-core
+    kernel's operand rounding is NOT required (different k order), so the comparison is by tolerance."""
+    rng = np.random.default_rng(140 + M)
+    Kd, Ns = 1024, (512, 256, 256)
+    a = (rng.standard_normal((M, Kd)) * 0.5).astype(np.float16)
+    mats = []
+    for n in Ns:
+        w = (rng.standard_normal((Kd, n)) * 0.3).astype(np.float16)
+        mats.append(O.quantize_q40(w, 64))
+    a_d = dev(a)
+    tiled = [(K.relayout_tiled(dev(q), dev(s), (Kd, n)), (Kd, n)) for (q, s), n in zip(mats, Ns)]
+    outs = K.gemm_tiled_tc(a_d, tiled, use_pdl=True)
+    for v, (q, s), n in zip(outs, mats, Ns):
+        assert_close(host(v), O.matmul_q40(a, q, s, (Kd, n)))
+
+
+def test_matmul_tiled_tc_selects_dequantised_rows(K):
+    """One-hot activation rows select exactly the dequantised weight rows (fp16(code * scale), the
+    reference's operand value) at a 7B layer shape with an unsplit and a split k range."""
+    torch.manual_seed(3)
+    for (N, Kd) in [(4096, 4096), (4096, 11008)]:
+        W = (torch.randn((Kd, N), device="cuda") * 0.02).to(torch.float16)
+        q, s = K.quantize_q40(W, 64)
+        deq = K.dequantize_q40(q, s, 64, (Kd, N), torch.float16)
+        rows = [0, 1, 17, 63, 64, Kd // 2 + 3, Kd - 1] + list(range(100, 111))
+        a = torch.zeros((len(rows), Kd), dtype=torch.float16, device="cuda")
+        for i, r in enumerate(rows):
+            a[i, r] = 1.0
+        t = K.relayout_tiled(q, s, (Kd, N))
+        c = K.gemm_tiled_tc(a, [(t, (Kd, N))])[0]
+        assert torch.equal(c.view(torch.int16), deq[rows].view(torch.int16)), (N, Kd)
