@@ -778,7 +778,7 @@ def main():
     peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
 
     model = build_model(dev)
-    prefill_ms = None
+    prefill_ms = prefill_tiled_ms = None
     g = torch.Generator().manual_seed(1)
     prompt = torch.randint(0, VOCAB, (1, PROMPT_LEN), generator=g)
     with torch.inference_mode():
@@ -797,6 +797,17 @@ def main():
             pe1.record()
             torch.cuda.synchronize(dev)
             prefill_ms = pe0.elapsed_time(pe1)
+            # the same pass with the tensor-core matmul that reads the tiled weight copies
+            model.prefill_tiled_tc = True
+            model(ptok, 0)
+            torch.cuda.synchronize(dev)
+            pe0.record()
+            model(ptok, 0)
+            pe1.record()
+            torch.cuda.synchronize(dev)
+            prefill_tiled_ms = pe0.elapsed_time(pe1)
+            model.prefill_tiled_tc = False
+            model(ptok, 0)
         model.fork(0, 1, max(widths) - 1)
         torch.cuda.synchronize(dev)
 
@@ -878,6 +889,7 @@ def main():
             "e2e": {"value": e2e_tok_s[w0], "unit": UNIT, "h2d_bytes_per_step": e2e_res[w0][1],
                     "d2h_bytes_per_step": e2e_res[w0][2]},
             "prefill_ms": prefill_ms,      # prompt pass of PROMPT_LEN tokens (not part of the decode metric)
+            "prefill_tiled_tc_ms": prefill_tiled_ms,   # ... with Transformer.prefill_tiled_tc = True
             # this library's kernels enqueued inside the timed region of the headline width
             "gpu_launches": steps * launches[w0],
             "clocks": clocks,

@@ -4,19 +4,27 @@
 //
 // Swap-AB as in q40_gemm_tc.cu: the 256 output features of a span are the M dimension of two
 // tcgen05.mma accumulators (128 features each, in tensor memory), the batch rows the N dimension
-// (padded to a multiple of 16, up to 256).  What differs is how the operands arrive:
+// (padded to a multiple of 16, up to 128 per launch; wider batches go in row chunks).  What differs is how
+// the operands arrive:
 //   * one elected thread streams the weights: a 64-row k block of a span is 4 steps = 8704 contiguous
 //     bytes = ONE cp.async.bulk into a ring stage, and the matching 64-wide slice of the activations is
 //     ONE tiled TMA copy (cp.async.bulk.tensor.2d, 128-byte swizzle, rows beyond M zero-filled) into the
-//     same stage; both complete on the stage's mbarrier.  The ring is 3..6 stages deep, so 70..140 KB
+//     same stage; both complete on the stage's mbarrier.  The ring is up to 8 stages deep, so up to 200 KB
 //     are in flight per SM (the cp.async version held one block per producer group in flight and was
 //     bound by that);
-//   * eight dequantiser warps turn a stage's nibbles into the reference's operand value
-//     fp16(code * scale) (triton_kernels.py:444-445) and store them as a K-major, 128-byte-swizzled A
-//     operand (feature rows of 64 k): the tiled format hands every lane the four A-fragment words of
-//     mma.m16n8k16, i.e. per word rows g and g+8 at four consecutive k, which are two 8-byte stores;
-//   * one warp issues 2 x 4 tcgen05.mma per k block (K = 16 each) and commits the stage's and the A
-//     buffer's "free" mbarriers.
+//   * sixteen dequantiser warps (two sets that take the k blocks in turn) turn a stage's nibbles into the
+//     reference's operand value fp16(code * scale) (triton_kernels.py:444-445) and write it as the A
+//     operand straight into TENSOR MEMORY: the tiled format hands every lane the four A-fragment words of
+//     mma.m16n8k16 (rows g and g + 8 at four consecutive k per word), and that is the register layout of
+//     tcgen05.st.16x256b, so a warp stores two 16-row tiles x 64 k with two instructions and the
+//     dequantised weights never touch shared memory (through shared memory they cost 64 KB of traffic per
+//     k block, more than the operands themselves);
+//   * eight warps issue the tcgen05.mma (A from tensor memory, B from the stage): a k block is 2 x 4 MMAs of
+//     128 x Mpad x 16, small enough that the issuing thread's fixed latencies (mbarrier test, fences, commit:
+//     ~800 cycles per k block measured) dominate, so the k blocks alternate between two sets of four warps
+//     and each warp issues two MMAs per block; accumulators are zeroed beforehand so that every MMA
+//     accumulates and their order is free.  A commit per warp arrives on the block's "MMAs done" mbarrier,
+//     which frees both the stage and the A buffer.
 // The k range is split over a thread-block cluster; partial accumulators meet through distributed
 // shared memory (no global scratch).  Every mbarrier wait is bounded: on expiry the kernel records an
 // error code, skips the remaining work, frees its tensor memory and returns.
@@ -36,8 +44,9 @@ namespace q40 {
 namespace ttc {
 
 constexpr int DQ_WARPS = 16;                    // dequantiser warps: two sets of 8 that take the k blocks in turn
-constexpr int DQ_WARP0 = 4;                     // warp 0: copies, warps 1 and 2: MMA issue (one accumulator each),
-constexpr int THREADS = (DQ_WARP0 + DQ_WARPS) * 32;   // warp 3: idle, warps 4..19: dequantise
+constexpr int DQ_WARP0 = 4;                     // warp 0: copies, warps 1..3 and 20..24: MMA issue,
+constexpr int MMA_WARPS = 8;                    // warps 4..19: dequantise (aligned to the tensor-memory quadrants)
+constexpr int THREADS = (DQ_WARP0 + DQ_WARPS + MMA_WARPS - 3) * 32;
 constexpr int BK = 64;                          // k rows per pipeline stage
 constexpr int SPAN = 256;                       // output features per CTA
 constexpr int STEP_BYTES = 2048 + 128;
@@ -161,6 +170,12 @@ __device__ __forceinline__ void st_16x256b_x4(uint32_t taddr, const uint32_t (&r
 #define TTC_ROLE_FLUSH(kind) do { } while (0)
 #endif
 
+__device__ __forceinline__ void st_zero16(uint32_t taddr) {
+  const uint32_t z = 0u;
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1};"
+      ::"r"(taddr), "r"(z) : "memory");
+}
 // D[tmem] (+)= A[tmem] * B[smem descriptor]
 __device__ __forceinline__ void mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
   asm volatile(
@@ -192,21 +207,22 @@ gemm_tiled_tc_kernel(const Params p, const __grid_constant__ CUtensorMap amap) {
   const uint32_t raw0 = smem_u32(smem_raw);
   const uint32_t ring = (raw0 + 1023u) & ~1023u;
   unsigned char* gbase = smem_raw + (ring - raw0);
-  const size_t ring_bytes = max((size_t)S * stage_bytes, (size_t)p.Mpad * SPAN * 4);
+  const size_t ring_bytes = max((size_t)S * stage_bytes, ((size_t)p.Mpad * SPAN + 64) * 4);
   const uint32_t bars = ring + (uint32_t)ring_bytes;
   // full[s]: the stage's copies have landed; mdone[i % MAX_STAGES]: the MMAs of block i are complete (its
   // stage and its A buffer may be refilled); afull[ab]: the A buffer is written; done: all MMAs complete
   const uint32_t bar_full = bars, bar_mdone = bars + 8 * MAX_STAGES, bar_afull = bars + 16 * MAX_STAGES;
-  const uint32_t bar_done = bar_afull + 8 * NA;
-  unsigned char* tail = gbase + ring_bytes + 16 * MAX_STAGES + 8 * NA + 8;
+  const uint32_t bar_done = bar_afull + 8 * NA, bar_zero = bar_done + 8;
+  unsigned char* tail = gbase + ring_bytes + 16 * MAX_STAGES + 8 * NA + 16;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail);
   volatile int* s_failed = reinterpret_cast<volatile int*>(tail + 8);
 
   if (tid == 0) {
     *s_failed = 0;
-    for (int s = 0; s < MAX_STAGES; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_mdone + 8 * s, 2); }
+    for (int s = 0; s < MAX_STAGES; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_mdone + 8 * s, MMA_WARPS / 2); }
     for (int s = 0; s < NA; ++s) mbar_init(bar_afull + 8 * s, DQ_WARPS / 2);
-    mbar_init(bar_done, 2);
+    mbar_init(bar_done, MMA_WARPS);
+    mbar_init(bar_zero, DQ_WARPS);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -253,17 +269,22 @@ gemm_tiled_tc_kernel(const Params p, const __grid_constant__ CUtensorMap amap) {
       Q40_STAMP(3);
     }
     __syncwarp();
-  } else if (warp == 1 || warp == 2) {
-    // ================= the two MMA warps: lane 0 issues for accumulator hh, the warp stays converged =================
-    // (a tcgen05.mma costs its issuing thread ~50 cycles and an mbarrier test ~100, whatever the tile size, so
-    // one thread cannot feed 8 small MMAs per k block; the dequantisers' arrival on afull also covers the
-    // stage's copies, which they waited for)
+  } else if (warp < DQ_WARP0 || warp >= DQ_WARP0 + DQ_WARPS) {
+    // ================= the eight MMA warps: lane 0 issues, the warp stays converged =================
+    // Per k block an issuing warp spends ~800 cycles on fixed latencies (mbarrier test, fences, commit) and
+    // ~60-120 per tcgen05.mma, whatever the tile size, so one thread cannot feed eight small MMAs per k block:
+    // warp (set, hh, kp) issues the k steps 2 kp and 2 kp + 1 of accumulator hh for the k blocks of its set
+    // (even or odd).  Every MMA accumulates (the dequantisers zero the accumulators first), so the order in
+    // which the warps' MMAs reach the tensor core does not matter.  The dequantisers' arrival on afull also
+    // covers the stage's copies, which they waited for.
     // instruction descriptor: D fp32, A and B fp16 and K-major, N = Mpad, M = 128
-    const int hh = warp - 1;
+    const int mi = (warp < DQ_WARP0) ? warp - 1 : warp - (DQ_WARP0 + DQ_WARPS) + 3;
+    const int hh = (mi >> 1) & 1, kp = mi & 1, mset = mi >> 2;
     const uint32_t idesc = (1u << 4) | ((uint32_t)(p.Mpad >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (!mbar_wait(bar_zero, 0)) failed = true;
     TTC_ROLE_DECL
-    for (int i = 0; i < nblk; ++i) {
+    for (int i = mset; i < nblk && !failed; i += 2) {
       const int s = i % S, ab = i % NA;
       TTC_ROLE(1, i, 0);
       if (!mbar_wait(bar_afull + 8 * ab, (uint32_t)((i / NA) & 1))) { failed = true; break; }
@@ -273,19 +294,19 @@ gemm_tiled_tc_kernel(const Params p, const __grid_constant__ CUtensorMap amap) {
         const uint64_t bd0 = kmajor_desc(ring + s * stage_bytes + RAW_PAD);
         const uint32_t a0 = tmem + A_COL0 + ab * 64 + hh * 32;
 #pragma unroll
-        for (int ks = 0; ks < BK / 16; ++ks)
-          mma_ts(tmem + hh * ACC_COLS, a0 + ks * 8, bd0 + (uint64_t)((ks * 32) >> 4), idesc,
-                 (i > 0 || ks > 0) ? 1u : 0u);
+        for (int k2 = 0; k2 < 2; ++k2) {
+          const int ks = 2 * kp + k2;
+          mma_ts(tmem + hh * ACC_COLS, a0 + ks * 8, bd0 + (uint64_t)((ks * 32) >> 4), idesc, 1u);
+        }
         TTC_ROLE(1, i, 3);
         commit(bar_mdone + 8 * s);                  // the stage and the A buffer may be refilled when the MMAs
-        if (i == nblk - 1) commit(bar_done);        // of both warps are done
-      }
+      }                                             // of the set's four warps are done
       TTC_ROLE(1, i, 6);
       __syncwarp();
     }
+    if (lane == 0 && !failed) commit(bar_done);     // all of this thread's MMAs
+    __syncwarp();
     if (warp == 1) TTC_ROLE_FLUSH(312);
-  } else if (warp == 3) {
-    // idle: keeps the dequantiser warps aligned to the tensor-memory lane quadrants
   } else {
     // ================= dequantisers: a stage's nibbles -> A operand in tensor memory =================
     // A warp may touch only the 32 tensor-memory lanes of its quadrant (warp index mod 4) = 32 feature rows
@@ -296,6 +317,13 @@ gemm_tiled_tc_kernel(const Params p, const __grid_constant__ CUtensorMap amap) {
     const int t = lane & 3;
     const unsigned char* lane_w = gbase + (q * 32 + lane) * 16 + (quad & 1) * 8;     // words of tiles 2 (quad & 1), + 1
     const unsigned char* lane_s = gbase + 2048 + q * 32 + t * 8;
+    // zero this warp's lanes of accumulator hh (the sets take the 16-column chunks in turn)
+    for (int ch = dset; ch < p.Mpad / 16; ch += 2)
+      st_zero16(tmem + ((uint32_t)(32 * quad) << 16) + hh * ACC_COLS + ch * 16);
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_zero);
     TTC_ROLE_DECL
     for (int i = dset; i < nblk; i += 2) {                    // the set's k blocks
       const int s = i % S, ab = i % NA;
@@ -348,13 +376,14 @@ gemm_tiled_tc_kernel(const Params p, const __grid_constant__ CUtensorMap amap) {
   if (failed && tid == 0) atomicExch(p.err, 1);
   Q40_STAMP(4);
 
-  // ---- accumulators -> fp32 tile [Mpad][256] in shared memory -> split-K sum over the cluster through
-  // distributed shared memory -> fp16 store ----
+  // ---- accumulators -> fp32 tile [Mpad][256] in shared memory (over the ring, idle by now) -> split-K sum
+  // over the cluster through distributed shared memory: rank r finishes the r-th slice of the (m, feature)
+  // pairs, adding the ranks' tiles in rank order -> fp16 store ----
   float* tile_f = reinterpret_cast<float*>(gbase);
-  if (!failed && warp >= DQ_WARP0) {
+  if (!failed && warp >= DQ_WARP0 && warp < DQ_WARP0 + DQ_WARPS) {
     // TMEM lanes 32 quad .. + 31 of accumulator hh; the two sets take the 16-row chunks in turn
     const int quad = warp & 3, hh = ((warp - DQ_WARP0) >> 2) & 1, dset = (warp - DQ_WARP0) >> 3;
-    const int feat = hh * 128 + 32 * quad + lane;     // MMA row = feature of the half
+    const int feat = hh * 128 + 32 * quad + lane;     // MMA row = feature of the span
     const int nchunk = p.Mpad / 16;
     for (int ch = dset; ch < nchunk; ch += 2) {
       uint32_t r[16];
@@ -512,7 +541,7 @@ extern "C" int q40_gemm_tiled_tc_multi(int nmat, const void* a, int64_t lda, con
     if (stages < 2) return Q40_E_UNSUPPORTED;
     p.stages = stages;
     size_t ring_bytes = (size_t)stages * stage_bytes;
-    const size_t tile_f = (size_t)p.Mpad * SPAN * 4;
+    const size_t tile_f = ((size_t)p.Mpad * SPAN + 64) * 4;     // slices are rounded up to 4 elements per rank
     if (tile_f > ring_bytes) ring_bytes = tile_f;
     const size_t smem = fixed + ring_bytes;
     TtcKernel kern = gemm_tiled_tc_kernel;

@@ -401,10 +401,11 @@ def gemv_fused(mode: int, a: torch.Tensor, weights, *, norm_w=None, ss_in=None, 
     return outs
 
 
-def gemm_tiled_tc(a: torch.Tensor, weights, use_pdl: bool = False):
+def gemm_tiled_tc(a: torch.Tensor, weights, use_pdl: bool = False, err: Optional[torch.Tensor] = None):
     """[a @ deq(B_i)] for 1-3 (tiled copy, (K, N)) pairs sharing the activations a [M > 16, K] on the tensor
     cores (q40_gemm_tiled_tc_multi in include/q40b200.h); the outputs are column slices of one buffer.
-    Raises if a bounded wait inside the kernel expired."""
+    Raises if a bounded wait inside the kernel expired — unless the caller passes its own int32 device word
+    `err` (zeroed by the caller), which the kernel sets instead and the caller reads when it synchronises."""
     import ctypes
     dev = _need_cuda(a, *[w[0] for w in weights])
     M, K = a.shape
@@ -417,13 +418,15 @@ def gemm_tiled_tc(a: torch.Tensor, weights, use_pdl: bool = False):
     for N in Ns:
         outs.append(buf[:, c0:c0 + N])
         c0 += N
-    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    own_err = err is None
+    if own_err:
+        err = torch.zeros(1, dtype=torch.int32, device=dev)
     P = ctypes.c_void_p * n
     check(lib.q40_gemm_tiled_tc_multi(n, a.data_ptr(), a.stride(0), P(*[w[0].data_ptr() for w in weights]),
                                       P(*[o.data_ptr() for o in outs]), (ctypes.c_int64 * n)(*[buf.stride(0)] * n),
                                       (ctypes.c_int * n)(*Ns), M, K, err.data_ptr(), 1 if use_pdl else 0,
                                       _stream(dev)), "q40_gemm_tiled_tc_multi")
-    if int(err.item()) != 0:
+    if own_err and int(err.item()) != 0:
         raise Q40Error("gemm_tiled_tc: a bounded wait inside the kernel expired")
     return outs
 

@@ -213,6 +213,13 @@ class Transformer(nn.Module):
         self.max_cluster = 16
         # B <= 16: the fused matmuls read a rearranged ("tiled") copy of each weight, made on first use
         self.use_tiled = True
+        # B > 16 and the prompt pass: the tensor-core matmul that reads the same tiled copies (A operand
+        # written to tensor memory); False: the tensor-core matmul on the checkpoint layout
+        self.use_tiled_tc = True
+        # the prompt pass keeps the checkpoint-layout tensor-core matmul by default: the tiled-copy kernel sums
+        # k in a different order, which flips greedy tokens at near-ties against the 7B reference run
+        self.prefill_tiled_tc = False
+        self._tc_err = None         # device word the prompt pass's tensor-core launches set on a wait expiry
         # ... True: through the byte-balanced stream-K launch (one CTA per SM, bulk-copy ring, no clusters);
         # False: the cluster-reduced launch on the same tiled copies (faster on B200, the default)
         self.use_stream = False
@@ -273,9 +280,8 @@ class Transformer(nn.Module):
         for li, layer in enumerate(self.layers):
             att, ff = layer.attention, layer.feed_forward
             xn = K.rmsnorm(h, layer.attention_norm.weight, p.norm_eps)
-            xq = K.matmul_q40(xn, att.wq.w, att.wq.s, att.wq.kn()).view(S, H, D)
-            xk = K.matmul_q40(xn, att.wk.w, att.wk.s, att.wk.kn()).view(S, Hkv, D)
-            xv = K.matmul_q40(xn, att.wv.w, att.wv.s, att.wv.kn()).view(S, Hkv, D)
+            xq, xk, xv = self._mm(xn, [att.wq, att.wk, att.wv])
+            xq, xk, xv = xq.view(S, H, D), xk.view(S, Hkv, D), xv.view(S, Hkv, D)
             K.rope_(xq, pos, self._cos, self._sin)
             K.rope_(xk, pos, self._cos, self._sin)
             att.cache_prompt_k[:S] = xk
@@ -290,15 +296,27 @@ class Transformer(nn.Module):
                 v_ = v_.repeat_interleave(H // Hkv, dim=1)
             o = F.scaled_dot_product_attention(q_, k_, v_, is_causal=True)
             o = o[0].transpose(0, 1).reshape(S, H * D)
-            ao = self._all_reduce(K.matmul_q40(o.contiguous(), att.wo.w, att.wo.s, att.wo.kn()))
+            ao = self._all_reduce(self._mm(o.contiguous(), [att.wo])[0])
             hn, h = K.rmsnorm(h, layer.ffn_norm.weight, p.norm_eps, residual=ao)
-            a1 = K.matmul_q40(hn, ff.w1.w, ff.w1.s, ff.w1.kn())
-            a3 = K.matmul_q40(hn, ff.w3.w, ff.w3.s, ff.w3.kn())
-            f2 = self._all_reduce(K.matmul_q40(K.silu_mul(a1, a3), ff.w2.w, ff.w2.s, ff.w2.kn()))
+            a1, a3 = self._mm(hn, [ff.w1, ff.w3])
+            f2 = self._all_reduce(self._mm(K.silu_mul(a1, a3), [ff.w2])[0])
             h = h + f2
         self._prefix_len_dev.fill_(S)
+        if self._tc_err is not None and int(self._tc_err.item()) != 0:
+            raise K.Q40Error("prompt pass: a bounded wait inside a tensor-core matmul expired")
         hn = K.rmsnorm(h, self.norm.weight, p.norm_eps)
         return F.linear(hn, self.output.weight).to(DTYPE).view(1, S, -1)
+
+    def _mm(self, x, lins):
+        """[x @ deq(W_i)] for projections that share the activations x [M, K] (prompt pass): one tensor-core
+        launch on the tiled copies when the shapes allow it, matmul_q40 per projection otherwise."""
+        M = x.shape[0]
+        if (M > 16 and self.use_tiled and self.use_tiled_tc and self.prefill_tiled_tc and len(lins) <= 3 and
+                all(l.group_size == 64 and self._tileable(l) and l.kn()[0] % 64 == 0 for l in lins)):
+            if self._tc_err is None:
+                self._tc_err = torch.zeros(1, dtype=torch.int32, device=self.device)
+            return K.gemm_tiled_tc(x, [(t, l.kn()) for t, l in zip(self._tiled_of(lins), lins)], err=self._tc_err)
+        return [K.matmul_q40(x, l.w, l.s, l.kn(), group_size=l.group_size) for l in lins]
 
     # ------------------------------------------------------------------ decode
     def _step_buffers(self, B):
@@ -333,6 +351,30 @@ class Transformer(nn.Module):
         shapes allow it, one launch per matrix otherwise."""
         import ctypes
         M, n = x.shape[0], len(lins)
+        if M > 16 and self.use_tiled and self.use_tiled_tc and x.stride(0) % 8 == 0:
+            # matrices that have a tiled copy (N % 256 == 0) go through the tensor-core kernel that reads it;
+            # the others (e.g. one kv head per rank under 8-way tensor parallelism) keep the checkpoint layout
+            t_idx = [i for i, (l, o) in enumerate(zip(lins, outs))
+                     if l.group_size == 64 and self._tileable(l) and l.kn()[0] % 64 == 0 and o.stride(0) % 2 == 0]
+            if t_idx and len(t_idx) < n:
+                rest = [i for i in range(n) if i not in t_idx]
+                self._gemm_multi(bufs, x, [lins[i] for i in t_idx], [outs[i] for i in t_idx], st)
+                self.use_tiled_tc = False
+                try:
+                    self._gemm_multi(bufs, x, [lins[i] for i in rest], [outs[i] for i in rest], st)
+                finally:
+                    self.use_tiled_tc = True
+                return
+            if t_idx and n <= 3 and all(l.kn()[0] == lins[0].kn()[0] for l in lins):
+                P = ctypes.c_void_p * n
+                err = bufs["gemm_ws"].data_ptr() + 4096 - 4      # the error word q40_gemm_kn also uses
+                check(lib.q40_gemm_tiled_tc_multi(n, x.data_ptr(), x.stride(0),
+                                                  P(*[t.data_ptr() for t in self._tiled_of(lins)]),
+                                                  P(*[o.data_ptr() for o in outs]),
+                                                  (ctypes.c_int64 * n)(*[o.stride(0) for o in outs]),
+                                                  (ctypes.c_int * n)(*[l.kn()[1] for l in lins]), M, lins[0].kn()[0],
+                                                  err, 1 if self.use_pdl else 0, st), "q40_gemm_tiled_tc_multi")
+                return
         ok = M > 16 and n <= 3 and all(l.group_size == 64 and l.kn()[1] % 128 == 0 and l.kn()[0] % 64 == 0 and
                                        l.kn()[0] == lins[0].kn()[0] and o.stride(0) % 2 == 0
                                        for l, o in zip(lins, outs)) and x.stride(0) % 8 == 0
@@ -561,8 +603,7 @@ class Transformer(nn.Module):
             self._gemm_multi(bufs, bufs["ao"], [att.wo], [bufs["o"]], st)
             self._all_reduce(bufs["o"])
             self._norm(h, bufs["o"], layer.ffn_norm.weight, xn, st)
-            self._gemm_multi(bufs, xn, [ff.w1], [bufs["a1"]], st)
-            self._gemm_multi(bufs, xn, [ff.w3], [bufs["a3"]], st)
+            self._gemm_multi(bufs, xn, [ff.w1, ff.w3], [bufs["a1"], bufs["a3"]], st)
             check(lib.q40_silu_mul(bufs["a1"].data_ptr(), bufs["a3"].data_ptr(), bufs["g"].data_ptr(),
                                    bufs["g"].numel(), st), "q40_silu_mul")
             self._gemm_multi(bufs, bufs["g"], [ff.w2], [bufs["f"]], st)
@@ -613,7 +654,7 @@ class Transformer(nn.Module):
             return self._decode_body(B)
         key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster, self.use_stream,
                self.use_tiled, self.use_fused_attn, self.fused_attn_max_width, self.stream_smem_budget,
-               self.use_fused_tail)
+               self.use_fused_tail, self.use_tiled_tc)
         g = self._graphs.get(key)
         if g is None:
             # torch requires capture on a side stream after a warm-up run; with greedy feedback that run
@@ -631,7 +672,7 @@ class Transformer(nn.Module):
                     self.max_cluster = 8
                     key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster, self.use_stream,
                            self.use_tiled, self.use_fused_attn, self.fused_attn_max_width, self.stream_smem_budget,
-                           self.use_fused_tail)
+                           self.use_fused_tail, self.use_tiled_tc)
                     self._decode_body(B)
             torch.cuda.current_stream(self.device).wait_stream(s)
             torch.cuda.synchronize(self.device)

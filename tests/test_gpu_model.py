@@ -239,3 +239,21 @@ def test_q4_lm_head_option(small):
     # and it is a quantised version of the fp16 head, not something else
     rel = float((got - ref).norm() / ref.norm())
     assert rel < 0.2, rel
+
+
+def test_prefill_tiled_tc_matches_default_prefill(small):
+    """The prompt pass through the tiled-copy tensor-core matmul (prefill_tiled_tc) against the default
+    prompt pass on the same model and against the reference class's logits: same logits within the matmul
+    tolerance, same prompt cache."""
+    g = small
+    outs = []
+    for flag in (False, True):
+        m = build_model(g, False)
+        m.prefill_tiled_tc = flag
+        with torch.inference_mode():
+            lg = m(torch.from_numpy(g["prompt"]).cuda(), 0)
+        outs.append((lg[0].float().cpu().numpy(), m.layers[-1].attention.cache_prompt_k.float().cpu().numpy().copy()))
+    (l0, k0), (l1, k1) = outs
+    logits_close(l1[-1], g["prefill_logits_last"])
+    np.testing.assert_allclose(l1, l0, rtol=2e-2, atol=0.15)
+    np.testing.assert_allclose(k1, k0, rtol=2e-2, atol=2e-2)
