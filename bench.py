@@ -663,7 +663,11 @@ def run_kernel_sweep(args):
         return ts[len(ts) // 2], ts[len(ts) // 5], ts[4 * len(ts) // 5]
 
     rows = []
-    for (N, Kd) in ((4096, 4096), (11008, 4096), (4096, 11008), (32128, 4096)):
+    shapes = ((4096, 4096), (11008, 4096), (4096, 11008), (32128, 4096))
+    if args.sweep_shapes:
+        shapes = tuple(tuple(int(v) for v in s_.split("x")) for s_ in args.sweep_shapes.split(","))
+    sweep_m = tuple(int(v) for v in args.sweep_m.split(",")) if args.sweep_m else (1, 10, 100)
+    for (N, Kd) in shapes:
         ws = []
         for i in range(NW):
             w = (torch.randn((Kd, N), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.float16)
@@ -671,7 +675,7 @@ def run_kernel_sweep(args):
             ws.append((q, sc))
             del w
         tiled = [K.relayout_tiled(q, sc, (Kd, N)) for q, sc in ws] if N % 256 == 0 else None
-        for M in (1, 10, 100):
+        for M in sweep_m:
             a = torch.randn((M, Kd), generator=g, device=dev, dtype=torch.float16)
             byts = N * Kd * (0.5 + 2 / 64) + 2 * M * Kd + 2 * M * N
             flops = 2.0 * M * N * Kd
@@ -679,10 +683,19 @@ def run_kernel_sweep(args):
             if M <= 16 and tiled is not None:
                 variants.append(("gemv_tiled", lambda: [K.gemv_fused(0, a, [(t, None, (Kd, N))], tiled=True, use_pdl=True)
                                                         for t in tiled]))
+            if M > 16 and tiled is not None:
+                tc_err = torch.zeros(1, dtype=torch.int32, device=dev)
+                variants.append(("gemm_tiled_tc", lambda: [K.gemm_tiled_tc(a, [(t, (Kd, N))], use_pdl=True, err=tc_err)
+                                                           for t in tiled]))
             for name, fn in variants:
                 med, p20, p80 = timed(fn)
                 us = med / NW * 1e6
+                # the bound of a launch: the weight stream at the measured copy bandwidth or the padded
+                # batch on the tensor cores at the measured bf16 rate, whichever is longer
+                mpad = (M + 15) // 16 * 16
+                t_bound = max(N * Kd * (0.5 + 2 / 64) / (hbm * 1e9), 2.0 * mpad * N * Kd / (tf_peak * 1e12))
                 rows.append({"kernel": name, "N": N, "K": Kd, "M": M, "us": round(us, 2),
+                             "bound_us": round(t_bound * 1e6, 2), "frac_of_bound": round(t_bound / (med / NW), 3),
                              "us_p20_p80": [round(p20 / NW * 1e6, 2), round(p80 / NW * 1e6, 2)],
                              "GBs": round(byts / (med / NW) / 1e9, 1), "frac_hbm_measured": round(byts / (med / NW) / 1e9 / hbm, 3),
                              "frac_hbm_8000": round(byts / (med / NW) / 1e9 / 8000.0, 3),
@@ -733,6 +746,8 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--sweep-shapes", default="", help="--workload kernels: only these NxK shapes, e.g. 11008x4096")
+    ap.add_argument("--sweep-m", default="", help="--workload kernels: only these batch widths, e.g. 100")
     ap.add_argument("--widths", default=",".join(str(w) for w in WIDTHS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-extras", action="store_true",
