@@ -446,7 +446,7 @@ def measure_70b_tp(world, rank, dev, steps, warmup, n_layers=80, branches=64, hb
         torch.cuda.synchronize(dev)
         sec = e0.elapsed_time(e1) * 1e-3
         # the step's collectives alone: the same 2 * n_layers all-reduces of [B, 8192] fp16, from a graph
-        ar_ms = None
+        ar_ms = fused_ar_ms = None
         if world > 1:
             buf = torch.zeros((B, 8192), dtype=torch.float16, device=dev)
             side = torch.cuda.Stream(dev)
@@ -469,11 +469,45 @@ def measure_70b_tp(world, rank, dev, steps, warmup, n_layers=80, branches=64, hb
                 gr.replay()
             a1.record()
             torch.cuda.synchronize(dev)
-            t = torch.tensor([sec, a0.elapsed_time(a1) * 1e-3 / 4], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            sec, ar_ms = float(t[0].item()), float(t[1].item()) * 1e3
             del gr
+            # ... and the same number of fused launches (all-reduce + residual add + RMSNorm) over the peer-mapped buffers
+            fused_s = 0.0
+            if model._tp_peer is not None:
+                hh = torch.zeros((B, 8192), dtype=torch.float16, device=dev)
+                xx = torch.zeros((B, 8192), dtype=torch.float16, device=dev)
+                wn = torch.ones(8192, dtype=torch.float16, device=dev)
+
+                def fused_calls():
+                    st_ = torch.cuda.current_stream(dev).cuda_stream
+                    for _ in range(2 * n_layers):
+                        model._tp_peer.allreduce_norm(buf, hh, wn, xx, 1e-5, st_)
+                side.wait_stream(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(side):
+                    fused_calls()
+                torch.cuda.current_stream(dev).wait_stream(side)
+                torch.cuda.synchronize(dev)
+                gf = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gf):
+                    fused_calls()
+                for _ in range(2):
+                    gf.replay()
+                dist.barrier()
+                torch.cuda.synchronize(dev)
+                f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                f0.record()
+                for _ in range(4):
+                    gf.replay()
+                f1.record()
+                torch.cuda.synchronize(dev)
+                fused_s = f0.elapsed_time(f1) * 1e-3 / 4
+                del gf
+            t = torch.tensor([sec, a0.elapsed_time(a1) * 1e-3 / 4, fused_s], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            sec, ar_ms, fused_ar_ms = float(t[0].item()), float(t[1].item()) * 1e3, float(t[2].item()) * 1e3
+        tp_status = model.tp_status()
+        fused_ar = model._tp_peer is not None
         model.release_graphs()
+        model.release_tp_buffers()
         hid = model.layers[0].feed_forward.full_hidden_dim
     per_layer = (8192 * 8192 * 2 + 2 * 8192 * 1024 + 3 * 8192 * hid)
     wbytes = margs.n_layers * (per_layer // 2 + per_layer // 64 * 2) / world + VOCAB * 8192 * 2
@@ -486,8 +520,12 @@ def measure_70b_tp(world, rank, dev, steps, warmup, n_layers=80, branches=64, hb
             "branches": B, "prompt_len": P, "steps": steps, "warmup": warmup, "ms_per_step": sec / steps * 1e3,
             "tokens_per_s": B * steps / sec, "weight_bytes_per_gpu_per_step": wbytes,
             "weight_stream_gbs_per_gpu": gbs, "frac_of_hbm_peak_per_gpu": gbs / hbm_peak,
+            "allreduce": ("one fused launch (all-reduce + residual add + RMSNorm) over peer-mapped buffers"
+                          if fused_ar else "torch.distributed all_reduce (NCCL)"),
+            "fused_allreduce_wait_status": tp_status,
             "allreduces_per_step": 2 * margs.n_layers, "allreduce_bytes": B * 8192 * 2,
-            "allreduce_ms_per_step_alone": ar_ms}
+            "allreduce_ms_per_step_alone": ar_ms,                 # 160 NCCL all-reduces from a graph
+            "fused_allreduce_ms_per_step_alone": fused_ar_ms}     # 160 fused launches from a graph
 
 
 def finish_distributed(dev):

@@ -369,6 +369,30 @@ int q40_rope(void* x, const int32_t* pos, const void* cos_tbl, const void* sin_t
  * Replaces: F.silu(w1(x)) * w3(x) in FeedForward.forward (hf_model_q40_kv_shared.py:434). */
 int q40_silu_mul(const void* a, const void* b, void* y, int64_t n, void* stream);
 
+/* ---- tensor-parallel all-reduce fused with residual add and RMSNorm (no counterpart in the reference beyond
+ * the torch.distributed all_reduce after wo and w2, hf_model_q40_kv_shared.py:258-261) ----
+ * One process per GPU.  Every rank allocates one buffer (q40_tp_alloc: cudaMalloc + zero fill + CUDA IPC handle of
+ * 64 bytes), hands the handle to the other ranks by any host channel, and maps theirs (q40_tp_open).
+ * q40_tp_layout gives {offset of the receive areas, total bytes} for (world <= 8, max_rows, dim); a receive
+ * area is [2][world][max_rows][dim / 4] lines of 16 bytes {2 fp16, flag, 2 fp16, flag}.
+ * q40_tp_allreduce_norm, called by all ranks in the same order:
+ *   h[rows, dim] += fp16(sum over ranks of partial[rows, dim], fp32, rank order); xn = RMSNorm(h) * norm_w
+ * (norm_w / xn may be NULL).  The kernel pushes its partial rows into the peers' buffers with plain 16-byte
+ * stores that carry the call's sequence number as their flags (no fences), waits for the peers' lines at
+ * most `wait_cycles` SM cycles (<= 0: 2^31) and reduces locally; a wait that expires sets the status word
+ * (q40_tp_status: 1 + the missing rank) and the launch still ends.  `bufs` is a
+ * host array of `world` device pointers (own buffer at [rank]).  Capturable in a CUDA graph: the call's
+ * sequence number lives in the buffer. */
+int q40_tp_layout(int world, int max_rows, int dim, size_t* out2);
+int q40_tp_alloc(size_t bytes, void** ptr, void* handle64);
+int q40_tp_open(const void* handle64, void** ptr);
+int q40_tp_close(void* ptr);
+int q40_tp_free(void* ptr);
+int q40_tp_allreduce_norm(const void* partial, int64_t ldp, void* h, const void* norm_w, void* xn, int rows, int dim,
+                          float eps, int rank, int world, void* const* bufs, int max_rows, long long wait_cycles,
+                          void* stream);
+int q40_tp_status(void* own_buf, int* host_out, int clear, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

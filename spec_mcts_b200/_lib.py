@@ -46,6 +46,14 @@ SIGNATURES = {
                                c_void_p, c_void_p]),
     "q40_gemm_kn_tc_multi": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_int, c_int, c_void_p, c_int, c_void_p]),
+    "q40_tp_layout": (c_int, [c_int, c_int, c_int, c_void_p]),
+    "q40_tp_alloc": (c_int, [c_size_t, c_void_p, c_void_p]),
+    "q40_tp_open": (c_int, [c_void_p, c_void_p]),
+    "q40_tp_close": (c_int, [c_void_p]),
+    "q40_tp_free": (c_int, [c_void_p]),
+    "q40_tp_allreduce_norm": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int,
+                                      c_int, c_void_p, c_int, ctypes.c_longlong, c_void_p]),
+    "q40_tp_status": (c_int, [c_void_p, c_void_p, c_int, c_void_p]),
     "q40_gemm_tiled_tc_multi": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_int, c_int, c_void_p, c_int, c_void_p]),
     "q40_gemm_kn_static": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,

@@ -216,6 +216,11 @@ class Transformer(nn.Module):
         # B > 16 and the prompt pass: the tensor-core matmul that reads the same tiled copies (A operand
         # written to tensor memory); False: the tensor-core matmul on the checkpoint layout
         self.use_tiled_tc = True
+        # tensor parallel: all-reduce + residual add + RMSNorm as one launch over peer-mapped buffers (plain
+        # stores into the peers' memory); False: torch.distributed all_reduce + the norm kernel
+        self.use_tp_fused_allreduce = True
+        self.tp_wait_cycles = 0     # limit of the wait for a peer's rows in SM cycles (0: 2^31, about a second)
+        self._tp_peer = None
         # the prompt pass keeps the checkpoint-layout tensor-core matmul by default: the tiled-copy kernel sums
         # k in a different order, which flips greedy tokens at near-ties against the 7B reference run
         self.prefill_tiled_tc = False
@@ -582,9 +587,12 @@ class Transformer(nn.Module):
         pos, plen = self._pos_dev, self._prefix_len_dev
         aws = bufs["attn_ws"]
         pending = None     # output of the previous sub-block, added to h by the next norm kernel
-        for layer in self.layers:
+        peer = self._tp_peer_buffers() if self.tp_world > 1 and self.use_tp_fused_allreduce else None
+        normed = False     # xn already holds the attention norm of h (written by the fused all-reduce)
+        for li, layer in enumerate(self.layers):
             att, ff = layer.attention, layer.feed_forward
-            self._norm(h, pending, layer.attention_norm.weight, xn, st)
+            if not normed:
+                self._norm(h, pending, layer.attention_norm.weight, xn, st)
             self._gemm_multi(bufs, xn, [att.wq, att.wk, att.wv], [bufs["q"], bufs["k"], bufs["v"]], st)
             check(lib.q40_rope_kv_append(bufs["q"].data_ptr(), H * D, bufs["k"].data_ptr(), Hkv * D,
                                          bufs["v"].data_ptr(), Hkv * D, pos.data_ptr(), plen.data_ptr(),
@@ -601,20 +609,50 @@ class Transformer(nn.Module):
                                            bufs["ao"].data_ptr(), B, H, Hkv, D, aws.data_ptr(), aws.numel(), st),
                   "q40_attn_tree_decode")
             self._gemm_multi(bufs, bufs["ao"], [att.wo], [bufs["o"]], st)
-            self._all_reduce(bufs["o"])
-            self._norm(h, bufs["o"], layer.ffn_norm.weight, xn, st)
+            if peer is not None:
+                # all-reduce of the partial wo outputs + residual add + ffn norm: one launch
+                peer.allreduce_norm(bufs["o"], h, layer.ffn_norm.weight, xn, p.norm_eps, st, self.tp_wait_cycles)
+            else:
+                self._all_reduce(bufs["o"])
+                self._norm(h, bufs["o"], layer.ffn_norm.weight, xn, st)
             self._gemm_multi(bufs, xn, [ff.w1, ff.w3], [bufs["a1"], bufs["a3"]], st)
             check(lib.q40_silu_mul(bufs["a1"].data_ptr(), bufs["a3"].data_ptr(), bufs["g"].data_ptr(),
                                    bufs["g"].numel(), st), "q40_silu_mul")
             self._gemm_multi(bufs, bufs["g"], [ff.w2], [bufs["f"]], st)
-            self._all_reduce(bufs["f"])
-            pending = bufs["f"]
-        self._norm(h, pending, self.norm.weight, xn, st)
+            if peer is not None:
+                # ... of the partial w2 outputs + residual add + the next layer's attention norm (or the final norm)
+                nxt = self.layers[li + 1].attention_norm.weight if li + 1 < len(self.layers) else self.norm.weight
+                peer.allreduce_norm(bufs["f"], h, nxt, xn, p.norm_eps, st, self.tp_wait_cycles)
+                normed = True
+            else:
+                self._all_reduce(bufs["f"])
+                pending = bufs["f"]
+        if not normed:
+            self._norm(h, pending, self.norm.weight, xn, st)
         torch.matmul(xn, self.output.weight.t(), out=bufs["logits"])
         if self.greedy_feedback:
             self._tok_dev[:B].copy_(bufs["logits"].argmax(dim=-1))
             self._pos_dev[:B] += 1
         return bufs["logits"]
+
+    def _tp_peer_buffers(self):
+        """Peer-mapped buffers of the fused all-reduce launch (made on first use: a collective call)."""
+        if self._tp_peer is None:
+            from .tp_comm import PeerBuffers
+            self._tp_peer = PeerBuffers(self.tp_rank, self.tp_world, self.params.max_batch_size, self.params.dim,
+                                        self.device, group=self.tp_group)
+        return self._tp_peer
+
+    def tp_status(self) -> int:
+        """Non-zero if a bounded wait of a fused all-reduce launch expired (1 + the missing rank; synchronises)."""
+        return self._tp_peer.status() if self._tp_peer is not None else 0
+
+    def release_tp_buffers(self):
+        """Unmap and free the peer-mapped buffers (collective; after release_graphs, before the process group
+        is destroyed)."""
+        if self._tp_peer is not None:
+            self._tp_peer.close()
+            self._tp_peer = None
 
     def _all_reduce(self, t):
         """Sum the partial outputs of a row-parallel matmul over the tensor-parallel ranks."""
@@ -654,7 +692,7 @@ class Transformer(nn.Module):
             return self._decode_body(B)
         key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster, self.use_stream,
                self.use_tiled, self.use_fused_attn, self.fused_attn_max_width, self.stream_smem_budget,
-               self.use_fused_tail, self.use_tiled_tc)
+               self.use_fused_tail, self.use_tiled_tc, self.use_tp_fused_allreduce)
         g = self._graphs.get(key)
         if g is None:
             # torch requires capture on a side stream after a warm-up run; with greedy feedback that run
@@ -672,7 +710,7 @@ class Transformer(nn.Module):
                     self.max_cluster = 8
                     key = (B, self.greedy_feedback, self.use_fused, self.use_pdl, self.max_cluster, self.use_stream,
                            self.use_tiled, self.use_fused_attn, self.fused_attn_max_width, self.stream_smem_budget,
-                           self.use_fused_tail, self.use_tiled_tc)
+                           self.use_fused_tail, self.use_tiled_tc, self.use_tp_fused_allreduce)
                     self._decode_body(B)
             torch.cuda.current_stream(self.device).wait_stream(s)
             torch.cuda.synchronize(self.device)

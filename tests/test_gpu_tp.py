@@ -51,7 +51,7 @@ def _build(args, full, emb, out, rank, world, group):
     return m.to(dev, torch.float16)
 
 
-def _worker(rank, world, port, ret):
+def _worker(rank, world, port, ret, fused_allreduce):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -63,6 +63,7 @@ def _worker(rank, world, port, ret):
     full, emb, out = _full_checkpoint(args)
     with torch.inference_mode():
         tpm = _build(args, full, emb, out, rank, world, None)
+        tpm.use_tp_fused_allreduce = fused_allreduce
         ref = _build(args, full, emb, out, 0, 1, None) if rank == 0 else None
         if ref is not None:
             # the tensor-parallel step runs the checkpoint-layout kernels one by one; give the one-GPU
@@ -90,10 +91,15 @@ def _worker(rank, world, port, ret):
                 nxt = torch.zeros((3, 1), dtype=torch.int64, device="cuda")
             dist.broadcast(nxt, 0)
             toks, pos = nxt, pos + 1
+        status = tpm.tp_status()
         if rank == 0:
             ret["errs"] = errs
-        # graphs that captured NCCL collectives must be gone before the communicator is torn down
+            ret["status"] = status
+            ret["fused_buffers"] = tpm._tp_peer is not None
+        # graphs that captured NCCL collectives must be gone before the communicator is torn down; the
+        # peer-mapped buffers of the fused all-reduce are unmapped while the ranks can still meet
         tpm.release_graphs()
+        tpm.release_tp_buffers()
         if ref is not None:
             ref.release_graphs()
     import threading
@@ -102,15 +108,20 @@ def _worker(rank, world, port, ret):
     os._exit(0)
 
 
-def test_tp2_matches_single_gpu():
+@pytest.mark.parametrize("fused_allreduce", [True, False])
+def test_tp2_matches_single_gpu(fused_allreduce):
+    """fused_allreduce: the all-reduce + residual + RMSNorm launch over peer-mapped buffers (the default);
+    otherwise torch.distributed all_reduce (NCCL) and the norm kernel."""
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two CUDA devices")
     import torch.multiprocessing as mp
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     with mp.Manager() as mgr:
         ret = mgr.dict()
-        mp.spawn(_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+        mp.spawn(_worker, args=(2, _free_port(), ret, fused_allreduce), nprocs=2, join=True)
         errs = list(ret["errs"])
+        assert ret["status"] == 0, "a bounded wait of the fused all-reduce expired"
+        assert ret["fused_buffers"] == fused_allreduce
     print("relative L2 error of TP=2 logits vs one GPU:", np.round(errs, 4))
     # partial sums are rounded to fp16 before the all-reduce and the Q4_0 KV round trip can flip a
     # code (see tests/test_gpu_model.py), hence a statistical bound
