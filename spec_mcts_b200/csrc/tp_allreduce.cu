@@ -15,6 +15,11 @@
 //      launch always ends.  fp32 sum of the ranks' fp16 partials in rank order (the same order on every rank,
 //      so all ranks hold bit-identical residual streams), one rounding to fp16, fp16 residual add, RMSNorm
 //      with the reference's rounding points (hf_model_q40_kv_shared.py:129-134).
+// Two ranks exchange whole rows in one shot as described.  More than two ranks work in two shots, so that a
+// rank sends 2 (world - 1) / world rows' worth instead of world - 1: rank j receives column slice j of every
+// peer's partial row, sums it (rank order, fp32), adds the residual and pushes the finished slice to everybody;
+// every rank then holds the same finished row and normalises it.  (One shot at 8 ranks: 64 us per 1 MiB
+// reduction, slower than the library's 50 us.)
 // Receive areas are double-buffered by the parity of the sequence number: a rank can be at most one call
 // ahead of a peer, because it cannot finish call k + 1 before that peer has pushed call k + 1, which the peer
 // does only after it has consumed call k.  The sequence number lives in the rank's own buffer and is
@@ -82,66 +87,131 @@ allreduce_norm_kernel(const Params p) {
   const size_t row_lines = (size_t)p.dim / 4;
   const __half* mine = p.partial + (int64_t)r * p.ldp;
 
-  // ---- 1. push this rank's row into every peer's receive area [slot][this rank][row] ----
-  for (int q = 0; q < p.world; ++q) {
-    if (q == p.rank) continue;
-    uint4* dst = reinterpret_cast<uint4*>(p.bufs[q] + p.recv_off) +
-                 (((size_t)slot * p.world + p.rank) * p.max_rows + r) * row_lines;
-    for (int i = tid * 8; i < p.dim; i += THREADS * 8) {
-      const uint4 v = *reinterpret_cast<const uint4*>(mine + i);
-      st_line(dst + i / 4, make_uint4(v.x, (uint32_t)seq, v.y, (uint32_t)seq));
-      st_line(dst + i / 4 + 1, make_uint4(v.z, (uint32_t)seq, v.w, (uint32_t)seq));
-    }
-  }
-
-  // ---- 2. fp32 sum in rank order (waiting, bounded, for each peer line), one rounding, residual add ----
-  const uint4* recv = reinterpret_cast<const uint4*>(own + p.recv_off);
+  float ss = 0.f;
   __half* hr = p.h + (int64_t)r * p.dim;
   const long long t0 = clock64();
   bool gave_up = false;
-  float ss = 0.f;
-  for (int i = tid * 8; i < p.dim; i += THREADS * 8) {
-    float acc[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int q = 0; q < p.world; ++q) {
-      uint4 v;
-      if (q == p.rank) {
-        v = *reinterpret_cast<const uint4*>(mine + i);
-      } else {
-        const uint4* src = recv + (((size_t)slot * p.world + q) * p.max_rows + r) * row_lines + i / 4;
-        uint4 l0 = ld_line(src), l1 = ld_line(src + 1);
-        unsigned spins = 0;
-        while (!gave_up && !(l0.y == (uint32_t)seq && l0.w == (uint32_t)seq && l1.y == (uint32_t)seq && l1.w == (uint32_t)seq)) {
-          if ((++spins & 63u) == 0 && clock64() - t0 > p.wait_cycles) {
-            atomicExch(hdr + 2, 1 + q);     // status: 1 + the rank that did not arrive
-            gave_up = true;
-            break;
-          }
-          l0 = ld_line(src);
-          l1 = ld_line(src + 1);
-        }
-        v = make_uint4(l0.x, l0.z, l1.x, l1.z);
+  // a peer line: spin (bounded) until both flags show this call's sequence number
+  auto wait_lines = [&](const uint4* src, int q) -> uint4 {
+    uint4 l0 = ld_line(src), l1 = ld_line(src + 1);
+    unsigned spins = 0;
+    while (!gave_up && !(l0.y == (uint32_t)seq && l0.w == (uint32_t)seq && l1.y == (uint32_t)seq && l1.w == (uint32_t)seq)) {
+      if ((++spins & 63u) == 0 && clock64() - t0 > p.wait_cycles) {
+        atomicExch(hdr + 2, 1 + q);     // status: 1 + the rank that did not arrive
+        gave_up = true;
+        break;
       }
-      const __half2* vh = reinterpret_cast<const __half2*>(&v);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __half22float2(vh[j]);
-        acc[2 * j] += f.x;
-        acc[2 * j + 1] += f.y;
-      }
+      l0 = ld_line(src);
+      l1 = ld_line(src + 1);
     }
+    return make_uint4(l0.x, l0.z, l1.x, l1.z);
+  };
+  auto push_lines = [&](uint4* dst, uint4 v) {
+    st_line(dst, make_uint4(v.x, (uint32_t)seq, v.y, (uint32_t)seq));
+    st_line(dst + 1, make_uint4(v.z, (uint32_t)seq, v.w, (uint32_t)seq));
+  };
+  auto add8 = [](float (&acc)[8], uint4 v) {
+    const __half2* vh = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(vh[j]);
+      acc[2 * j] += f.x;
+      acc[2 * j + 1] += f.y;
+    }
+  };
+  // residual add of 8 columns (fp16 add, one rounding), sum of squares, store to h and to the row buffer
+  auto finish8 = [&](int i, const float (&acc)[8]) -> uint4 {
     uint4 hv = *reinterpret_cast<const uint4*>(hr + i);
     __half2* hh = reinterpret_cast<__half2*>(&hv);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      hh[j] = __hadd2(hh[j], __floats2half2_rn(acc[2 * j], acc[2 * j + 1]));   // fp16 add, one rounding
+      hh[j] = __hadd2(hh[j], __floats2half2_rn(acc[2 * j], acc[2 * j + 1]));
       const float2 f = __half22float2(hh[j]);
       ss = fmaf(f.x, f.x, ss);
       ss = fmaf(f.y, f.y, ss);
     }
     *reinterpret_cast<uint4*>(hr + i) = hv;
     *reinterpret_cast<uint4*>(row + i) = hv;
+    return hv;
+  };
+
+  if (p.world <= 2) {
+    // ================= one shot: every rank gets every rank's whole row =================
+    // ---- 1. push this rank's row into every peer's receive area [slot][this rank][row] ----
+    for (int q = 0; q < p.world; ++q) {
+      if (q == p.rank) continue;
+      uint4* dst = reinterpret_cast<uint4*>(p.bufs[q] + p.recv_off) +
+                   (((size_t)slot * p.world + p.rank) * p.max_rows + r) * row_lines;
+      for (int i = tid * 8; i < p.dim; i += THREADS * 8)
+        push_lines(dst + i / 4, *reinterpret_cast<const uint4*>(mine + i));
+    }
+    // ---- 2. fp32 sum in rank order (waiting, bounded, for each peer line), one rounding, residual add ----
+    const uint4* recv = reinterpret_cast<const uint4*>(own + p.recv_off);
+    for (int i = tid * 8; i < p.dim; i += THREADS * 8) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int q = 0; q < p.world; ++q) {
+        const uint4 v = (q == p.rank)
+            ? *reinterpret_cast<const uint4*>(mine + i)
+            : wait_lines(recv + (((size_t)slot * p.world + q) * p.max_rows + r) * row_lines + i / 4, q);
+        add8(acc, v);
+      }
+      finish8(i, acc);
+    }
+  } else {
+    // ================= two shots: rank j sums columns [j dim / world, (j + 1) dim / world) of every row and
+    // hands the finished slice (residual already added) to everybody =================
+    // areas: scatter [slot][source rank][row][slice lines], then gather with the same shape
+    const int ls = p.dim / p.world;                         // slice length in columns (a multiple of 8)
+    const size_t slice_lines = (size_t)ls / 4;
+    const size_t area_lines = (size_t)2 * p.world * p.max_rows * slice_lines;
+    auto scatter_of = [&](unsigned char* buf) { return reinterpret_cast<uint4*>(buf + p.recv_off); };
+    auto gather_of = [&](unsigned char* buf) { return reinterpret_cast<uint4*>(buf + p.recv_off) + area_lines; };
+    const size_t my_src = (((size_t)slot * p.world + p.rank) * p.max_rows + r) * slice_lines;   // as a source in a peer's area
+    const int chunks = ls / 8;
+    // ---- 1. push slice q of this rank's partial row to rank q ----
+    for (int e = tid; e < (p.world - 1) * chunks; e += THREADS) {
+      int q = e / chunks;
+      const int c = e % chunks;
+      if (q >= p.rank) ++q;
+      push_lines(scatter_of(p.bufs[q]) + my_src + 2 * c, *reinterpret_cast<const uint4*>(mine + q * ls + 8 * c));
+    }
+    // ---- 2. own slice: fp32 sum in rank order, one rounding, residual add; push the result to every peer ----
+    const uint4* sc_in = scatter_of(own);
+    for (int c = tid; c < chunks; c += THREADS) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      const int i = p.rank * ls + 8 * c;
+      for (int q = 0; q < p.world; ++q) {
+        const uint4 v = (q == p.rank)
+            ? *reinterpret_cast<const uint4*>(mine + i)
+            : wait_lines(sc_in + (((size_t)slot * p.world + q) * p.max_rows + r) * slice_lines + 2 * c, q);
+        add8(acc, v);
+      }
+      const uint4 hv = finish8(i, acc);
+      for (int q = 0; q < p.world; ++q)
+        if (q != p.rank) push_lines(gather_of(p.bufs[q]) + my_src + 2 * c, hv);
+    }
+    // ---- 3. the other ranks' finished slices ----
+    const uint4* ga_in = gather_of(own);
+    for (int e = tid; e < (p.world - 1) * chunks; e += THREADS) {
+      int q = e / chunks;
+      const int c = e % chunks;
+      if (q >= p.rank) ++q;
+      const uint4 hv = wait_lines(ga_in + (((size_t)slot * p.world + q) * p.max_rows + r) * slice_lines + 2 * c, q);
+      const int i = q * ls + 8 * c;
+      const __half2* hh = reinterpret_cast<const __half2*>(&hv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(hh[j]);
+        ss = fmaf(f.x, f.x, ss);
+        ss = fmaf(f.y, f.y, ss);
+      }
+      *reinterpret_cast<uint4*>(hr + i) = hv;
+      *reinterpret_cast<uint4*>(row + i) = hv;
+    }
   }
   if (p.norm_w != nullptr) {
     ss = warp_sum(ss);
@@ -238,6 +308,7 @@ extern "C" int q40_tp_allreduce_norm(const void* partial, int64_t ldp, void* h, 
   if (norm_w && !xn) return Q40_E_NULL;
   if (world < 1 || world > MAX_WORLD || rank < 0 || rank >= world) return Q40_E_SHAPE;
   if (rows < 1 || rows > max_rows || dim < 8 || dim % 8 != 0 || ldp < dim || ldp % 8 != 0) return Q40_E_SHAPE;
+  if (world > 2 && dim % (8 * world) != 0) return Q40_E_SHAPE;      // column slices of whole 16-byte chunks
   if (!q40_aligned(partial, 16) || !q40_aligned(h, 16) || (norm_w && !q40_aligned(norm_w, 16)) ||
       (xn && !q40_aligned(xn, 16)))
     return Q40_E_ALIGN;
