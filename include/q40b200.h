@@ -369,6 +369,13 @@ int q40_rope(void* x, const int32_t* pos, const void* cos_tbl, const void* sin_t
  * Replaces: F.silu(w1(x)) * w3(x) in FeedForward.forward (hf_model_q40_kv_shared.py:434). */
 int q40_silu_mul(const void* a, const void* b, void* y, int64_t n, void* stream);
 
+/* Causal attention of the prompt pass: o[S, H*128] = softmax over j <= i of q_i . k_j / sqrt(128), times v, per head,
+ * for S positions at once; q / o rows hold H heads, k / v rows Hkv heads (H % Hkv == 0, grouped-query heads
+ * read their kv head directly); ld* are row strides in elements.  Replaces the masked
+ * scaled_dot_product_attention of hf_model_q40_kv_shared.py:375-405 (mask built at :499-504). */
+int q40_attn_causal(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, void* o,
+                    int64_t ldo, int S, int H, int Hkv, int D, void* stream);
+
 /* ---- tensor-parallel all-reduce fused with residual add and RMSNorm (no counterpart in the reference beyond
  * the torch.distributed all_reduce after wo and w2, hf_model_q40_kv_shared.py:258-261) ----
  * One process per GPU.  Every rank allocates one buffer (q40_tp_alloc: cudaMalloc + zero fill + CUDA IPC handle of

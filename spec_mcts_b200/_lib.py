@@ -46,6 +46,8 @@ SIGNATURES = {
                                c_void_p, c_void_p]),
     "q40_gemm_kn_tc_multi": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_int, c_int, c_void_p, c_int, c_void_p]),
+    "q40_attn_causal": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int,
+                                c_int, c_int, c_int, c_void_p]),
     "q40_tp_layout": (c_int, [c_int, c_int, c_int, c_void_p]),
     "q40_tp_alloc": (c_int, [c_size_t, c_void_p, c_void_p]),
     "q40_tp_open": (c_int, [c_void_p, c_void_p]),

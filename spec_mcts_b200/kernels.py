@@ -401,6 +401,22 @@ def gemv_fused(mode: int, a: torch.Tensor, weights, *, norm_w=None, ss_in=None, 
     return outs
 
 
+def causal_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of a prompt: q [S, H, 128], k / v [S, Hkv, 128] (position-major, last two dims
+    contiguous) -> [S, H, 128]; position i attends positions 0..i (q40_attn_causal in include/q40b200.h)."""
+    dev = _need_cuda(q, k, v)
+    S, H, D = q.shape
+    Hkv = k.shape[1]
+    for t in (q, k, v):
+        if t.dtype != torch.float16 or t.stride(2) != 1 or t.stride(1) != D:
+            raise Q40Error("causal_attn: fp16 tensors [S, heads, 128] with contiguous heads expected")
+    if out is None:
+        out = torch.empty((S, H, D), dtype=torch.float16, device=dev)
+    check(lib.q40_attn_causal(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+                              out.data_ptr(), out.stride(0), S, H, Hkv, D, _stream(dev)), "q40_attn_causal")
+    return out
+
+
 def gemm_tiled_tc(a: torch.Tensor, weights, use_pdl: bool = False, err: Optional[torch.Tensor] = None):
     """[a @ deq(B_i)] for 1-3 (tiled copy, (K, N)) pairs sharing the activations a [M > 16, K] on the tensor
     cores (q40_gemm_tiled_tc_multi in include/q40b200.h); the outputs are column slices of one buffer.

@@ -292,16 +292,9 @@ class Transformer(nn.Module):
             att.cache_prompt_k[:S] = xk
             att.cache_prompt_v[:S] = xv
             att.cache_prompt_len = S
-            # causal attention over the prompt: dense batched attention is library territory
-            q_ = xq.transpose(0, 1).unsqueeze(0)
-            k_ = xk.transpose(0, 1).unsqueeze(0)
-            v_ = xv.transpose(0, 1).unsqueeze(0)
-            if Hkv != H:
-                k_ = k_.repeat_interleave(H // Hkv, dim=1)
-                v_ = v_.repeat_interleave(H // Hkv, dim=1)
-            o = F.scaled_dot_product_attention(q_, k_, v_, is_causal=True)
-            o = o[0].transpose(0, 1).reshape(S, H * D)
-            ao = self._all_reduce(self._mm(o.contiguous(), [att.wo])[0])
+            # causal attention over the prompt (grouped-query heads read their kv head directly)
+            o = K.causal_attn(xq, xk, xv).view(S, H * D)
+            ao = self._all_reduce(self._mm(o, [att.wo])[0])
             hn, h = K.rmsnorm(h, layer.ffn_norm.weight, p.norm_eps, residual=ao)
             a1, a3 = self._mm(hn, [ff.w1, ff.w3])
             f2 = self._all_reduce(self._mm(K.silu_mul(a1, a3), [ff.w2])[0])

@@ -525,3 +525,24 @@ def test_matmul_tiled_tc_selects_dequantised_rows(K):
         t = K.relayout_tiled(q, s, (Kd, N))
         c = K.gemm_tiled_tc(a, [(t, (Kd, N))])[0]
         assert torch.equal(c.view(torch.int16), deq[rows].view(torch.int16)), (N, Kd)
+
+
+@pytest.mark.parametrize("S,H,Hkv", [(1, 2, 2), (17, 4, 2), (64, 2, 1), (100, 4, 4), (129, 8, 2), (512, 32, 32), (700, 8, 1)])
+def test_causal_attention_matches_fp32_reference(K, S, H, Hkv):
+    """The prompt pass's causal attention against an fp32 torch computation of the same formula (the
+    reference calls scaled_dot_product_attention with a triangular mask, hf_model_q40_kv_shared.py:405,
+    499-504): ragged last blocks, one position, grouped-query heads, strided inputs."""
+    g = torch.Generator(device="cuda").manual_seed(S * 31 + H)
+    qkv = torch.randn((S, (H + 2 * Hkv) * 128), generator=g, device="cuda").half()
+    q = qkv[:, :H * 128].view(S, H, 128)                 # strided views of one buffer, as the prompt pass makes them
+    k = qkv[:, H * 128:(H + Hkv) * 128].view(S, Hkv, 128)
+    v = qkv[:, (H + Hkv) * 128:].view(S, Hkv, 128)
+    o = K.causal_attn(q, k, v)
+    rep = H // Hkv
+    qf = q.float().permute(1, 0, 2)
+    kf = k.float().permute(1, 0, 2).repeat_interleave(rep, dim=0)
+    vf = v.float().permute(1, 0, 2).repeat_interleave(rep, dim=0)
+    s = qf @ kf.transpose(1, 2) / np.sqrt(128.0)
+    s = s.masked_fill(torch.ones((S, S), device="cuda", dtype=torch.bool).triu(1), float("-inf"))
+    ref = (torch.softmax(s, dim=-1) @ vf).permute(1, 0, 2)
+    assert_close(host(o), ref.cpu().numpy().astype(np.float16))
