@@ -354,6 +354,18 @@ class Transformer(nn.Module):
             # the others (e.g. one kv head per rank under 8-way tensor parallelism) keep the checkpoint layout
             t_idx = [i for i, (l, o) in enumerate(zip(lins, outs))
                      if l.group_size == 64 and self._tileable(l) and l.kn()[0] % 64 == 0 and o.stride(0) % 2 == 0]
+            if len(t_idx) < n and self._concat_tileable(lins, outs):
+                # widths that cannot be tiled one by one (a kv head per rank: 128 columns) but whose outputs are
+                # adjacent column ranges of one buffer: one tiled copy of the concatenated matrix, one launch
+                cat = self._tiled_concat(lins)
+                err = bufs["gemm_ws"].data_ptr() + 4096 - 4
+                P1 = ctypes.c_void_p * 1
+                check(lib.q40_gemm_tiled_tc_multi(1, x.data_ptr(), x.stride(0), P1(cat.data_ptr()),
+                                                  P1(outs[0].data_ptr()), (ctypes.c_int64 * 1)(outs[0].stride(0)),
+                                                  (ctypes.c_int * 1)(sum(l.kn()[1] for l in lins)), M,
+                                                  lins[0].kn()[0], err, 1 if self.use_pdl else 0, st),
+                      "q40_gemm_tiled_tc_multi")
+                return
             if t_idx and len(t_idx) < n:
                 rest = [i for i in range(n) if i not in t_idx]
                 self._gemm_multi(bufs, x, [lins[i] for i in t_idx], [outs[i] for i in t_idx], st)
@@ -408,6 +420,35 @@ class Transformer(nn.Module):
                 l._tiled_src = l.w.data_ptr()
             out.append(l._tiled)
         return out
+
+    @staticmethod
+    def _concat_tileable(lins, outs):
+        """The matrices share K and the group size, their widths are whole 128-column packed blocks that add
+        up to whole 256-column spans, and their outputs are consecutive column ranges of one row-major buffer."""
+        Kd = lins[0].kn()[0]
+        if Kd % 64 != 0 or any(l.group_size != 64 or l.kn()[0] != Kd or l.kn()[1] % 128 != 0 for l in lins):
+            return False
+        if sum(l.kn()[1] for l in lins) % 256 != 0 or outs[0].stride(0) % 2 != 0:
+            return False
+        ptr = outs[0].data_ptr()
+        for l, o in zip(lins, outs):
+            if o.data_ptr() != ptr or o.stride(0) != outs[0].stride(0) or o.stride(1) != 1:
+                return False
+            ptr += l.kn()[1] * o.element_size()
+        return True
+
+    def _tiled_concat(self, lins):
+        """Tiled copy of [W_0 | W_1 | ...] (columns concatenated): packed rows and scale rows of the checkpoint
+        layout concatenate block by block, so no code or scale changes.  Cached on the first matrix."""
+        key = tuple(l.w.data_ptr() for l in lins)
+        first = lins[0]
+        if getattr(first, "_tiled_cat_key", None) != key:
+            Kd = first.kn()[0]
+            w = torch.cat([l.w.reshape(Kd, l.kn()[1] // 2) for l in lins], dim=1).contiguous()
+            sc = torch.cat([l.s.reshape(Kd, l.kn()[1] // 64) for l in lins], dim=1).contiguous()
+            first._tiled_cat = K.relayout_tiled(w, sc, (Kd, sum(l.kn()[1] for l in lins)))
+            first._tiled_cat_key = key
+        return first._tiled_cat
 
     def _streamable(self, lins, M):
         return self.use_tiled and self.use_stream and M <= 16 and all(self._tileable(l) for l in lins)
@@ -586,19 +627,22 @@ class Transformer(nn.Module):
             att, ff = layer.attention, layer.feed_forward
             if not normed:
                 self._norm(h, pending, layer.attention_norm.weight, xn, st)
-            self._gemm_multi(bufs, xn, [att.wq, att.wk, att.wv], [bufs["q"], bufs["k"], bufs["v"]], st)
-            check(lib.q40_rope_kv_append(bufs["q"].data_ptr(), H * D, bufs["k"].data_ptr(), Hkv * D,
-                                         bufs["v"].data_ptr(), Hkv * D, pos.data_ptr(), plen.data_ptr(),
+            qkv = bufs["qkv"]
+            Wq = (H + 2 * Hkv) * D
+            bq, bk, bv = qkv[:, :H * D], qkv[:, H * D:(H + Hkv) * D], qkv[:, (H + Hkv) * D:]
+            self._gemm_multi(bufs, xn, [att.wq, att.wk, att.wv], [bq, bk, bv], st)
+            check(lib.q40_rope_kv_append(bq.data_ptr(), Wq, bk.data_ptr(), Wq,
+                                         bv.data_ptr(), Wq, pos.data_ptr(), plen.data_ptr(),
                                          self._cos.data_ptr(), self._sin.data_ptr(), self._n_pos,
                                          att.cache_k.data_ptr(), att.cache_k_s.data_ptr(),
                                          att.cache_v.data_ptr(), att.cache_v_s.data_ptr(), B, H, Hkv, D,
                                          p.max_seq_len, st), "q40_rope_kv_append")
             pk, pv = att.cache_prompt_k, att.cache_prompt_v
-            check(lib.q40_attn_tree_decode(bufs["q"].data_ptr(), H * D, pk.data_ptr(), pv.data_ptr(),
+            check(lib.q40_attn_tree_decode(bq.data_ptr(), Wq, pk.data_ptr(), pv.data_ptr(),
                                            p.max_prompt_seq_len, plen.data_ptr(), pk.stride(0), pk.stride(1),
                                            att.cache_k.data_ptr(), att.cache_k_s.data_ptr(),
                                            att.cache_v.data_ptr(), att.cache_v_s.data_ptr(), p.max_seq_len,
-                                           pos.data_ptr(), bufs["k"].data_ptr(), bufs["v"].data_ptr(), Hkv * D,
+                                           pos.data_ptr(), bk.data_ptr(), bv.data_ptr(), Wq,
                                            bufs["ao"].data_ptr(), B, H, Hkv, D, aws.data_ptr(), aws.numel(), st),
                   "q40_attn_tree_decode")
             self._gemm_multi(bufs, bufs["ao"], [att.wo], [bufs["o"]], st)

@@ -257,3 +257,35 @@ def test_prefill_tiled_tc_matches_default_prefill(small):
     logits_close(l1[-1], g["prefill_logits_last"])
     np.testing.assert_allclose(l1, l0, rtol=2e-2, atol=0.15)
     np.testing.assert_allclose(k1, k0, rtol=2e-2, atol=2e-2)
+
+
+def test_wide_step_with_one_kv_head_uses_the_concatenated_tiled_copy():
+    """A geometry whose wk / wv are 128 columns wide (one kv head, as a rank of the 70B model holds under
+    8-way tensor parallelism): they cannot be tiled one by one, so the wide decode step multiplies by the
+    tiled copy of [wq | wk | wv].  Checked against the same model on the checkpoint-layout kernels."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from spec_mcts_b200.model import ModelArgs, Transformer, random_init_
+    args = ModelArgs(dim=512, n_layers=2, n_heads=4, n_kv_heads=1, vocab_size=512, multiple_of=256,
+                     max_batch_size=24, max_seq_len=8, max_prompt_seq_len=32)
+    B = 20
+    logits = []
+    with torch.inference_mode():
+        for tiled_tc in (True, False):
+            m = Transformer(args, device=torch.device("cuda"))
+            random_init_(m, seed=5, std=0.05)
+            m = m.to("cuda", torch.float16)
+            m.use_tiled_tc = tiled_tc
+            att = m.layers[0].attention
+            lins, outs = [att.wq, att.wk, att.wv], None
+            g = torch.Generator().manual_seed(2)
+            prompt = torch.randint(0, 512, (1, 9), generator=g).cuda()
+            m(prompt, 0)
+            m.fork(0, 1, B - 1)
+            toks = torch.randint(0, 512, (B, 1), generator=g).cuda()
+            lg = m(toks, 9)[:, -1].float().cpu().numpy()
+            logits.append(lg)
+            if tiled_tc:
+                assert not m._tileable(att.wk) and getattr(att.wq, "_tiled_cat", None) is not None
+    rel = np.linalg.norm(logits[0] - logits[1], axis=-1) / np.linalg.norm(logits[1], axis=-1)
+    assert rel.max() < 2e-2, rel
