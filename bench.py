@@ -722,9 +722,10 @@ def run_kernel_sweep(args):
                 variants.append(("gemv_tiled", lambda: [K.gemv_fused(0, a, [(t, None, (Kd, N))], tiled=True, use_pdl=True)
                                                         for t in tiled]))
             if M > 16 and tiled is not None:
-                tc_err = torch.zeros(1, dtype=torch.int32, device=dev)
-                variants.append(("gemm_tiled_tc", lambda: [K.gemm_tiled_tc(a, [(t, (Kd, N))], use_pdl=True, err=tc_err)
-                                                           for t in tiled]))
+                # matmul_q40 reads its own tiled copies above 16 rows too; the checkpoint-layout tensor-core
+                # kernel it used before is timed beside it
+                variants.append(("matmul_q40_checkpoint_layout",
+                                 lambda: [K.matmul_q40(a, q, sc, (Kd, N), relayout=False) for q, sc in ws]))
             for name, fn in variants:
                 med, p20, p80 = timed(fn)
                 us = med / NW * 1e6

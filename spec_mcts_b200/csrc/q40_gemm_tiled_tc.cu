@@ -19,12 +19,12 @@
 //     tcgen05.st.16x256b, so a warp stores two 16-row tiles x 64 k with two instructions and the
 //     dequantised weights never touch shared memory (through shared memory they cost 64 KB of traffic per
 //     k block, more than the operands themselves);
-//   * eight warps issue the tcgen05.mma (A from tensor memory, B from the stage): a k block is 2 x 4 MMAs of
+//   * four warps issue the tcgen05.mma (A from tensor memory, B from the stage): a k block is 2 x 4 MMAs of
 //     128 x Mpad x 16, small enough that the issuing thread's fixed latencies (mbarrier test, fences, commit:
-//     ~800 cycles per k block measured) dominate, so the k blocks alternate between two sets of four warps
-//     and each warp issues two MMAs per block; accumulators are zeroed beforehand so that every MMA
-//     accumulates and their order is free.  A commit per warp arrives on the block's "MMAs done" mbarrier,
-//     which frees both the stage and the A buffer.
+//     ~800 cycles per k block measured) matter, so each accumulator has two issuing warps that alternate k
+//     blocks and hand over in order through shared memory (every accumulator sees its MMAs in k order:
+//     results do not depend on which warp was faster).  A commit per warp arrives on the block's "MMAs done"
+//     mbarrier, which frees both the stage and the A buffer.
 // The k range is split over a thread-block cluster; partial accumulators meet through distributed
 // shared memory (no global scratch).  Every mbarrier wait is bounded: on expiry the kernel records an
 // error code, skips the remaining work, frees its tensor memory and returns.
@@ -44,8 +44,8 @@ namespace q40 {
 namespace ttc {
 
 constexpr int DQ_WARPS = 16;                    // dequantiser warps: two sets of 8 that take the k blocks in turn
-constexpr int DQ_WARP0 = 4;                     // warp 0: copies, warps 1..3 and 20..24: MMA issue,
-constexpr int MMA_WARPS = 8;                    // warps 4..19: dequantise (aligned to the tensor-memory quadrants)
+constexpr int DQ_WARP0 = 4;                     // warp 0: copies, warps 1..3 and 20: MMA issue,
+constexpr int MMA_WARPS = 4;                    // warps 4..19: dequantise (aligned to the tensor-memory quadrants)
 constexpr int THREADS = (DQ_WARP0 + DQ_WARPS + MMA_WARPS - 3) * 32;
 constexpr int BK = 64;                          // k rows per pipeline stage
 constexpr int SPAN = 256;                       // output features per CTA
@@ -170,12 +170,6 @@ __device__ __forceinline__ void st_16x256b_x4(uint32_t taddr, const uint32_t (&r
 #define TTC_ROLE_FLUSH(kind) do { } while (0)
 #endif
 
-__device__ __forceinline__ void st_zero16(uint32_t taddr) {
-  const uint32_t z = 0u;
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1};"
-      ::"r"(taddr), "r"(z) : "memory");
-}
 // D[tmem] (+)= A[tmem] * B[smem descriptor]
 __device__ __forceinline__ void mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
   asm volatile(
@@ -212,17 +206,19 @@ gemm_tiled_tc_kernel(const Params p, const __grid_constant__ CUtensorMap amap) {
   // full[s]: the stage's copies have landed; mdone[i % MAX_STAGES]: the MMAs of block i are complete (its
   // stage and its A buffer may be refilled); afull[ab]: the A buffer is written; done: all MMAs complete
   const uint32_t bar_full = bars, bar_mdone = bars + 8 * MAX_STAGES, bar_afull = bars + 16 * MAX_STAGES;
-  const uint32_t bar_done = bar_afull + 8 * NA, bar_zero = bar_done + 8;
+  const uint32_t bar_done = bar_afull + 8 * NA;
   unsigned char* tail = gbase + ring_bytes + 16 * MAX_STAGES + 8 * NA + 16;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail);
   volatile int* s_failed = reinterpret_cast<volatile int*>(tail + 8);
+  volatile int* s_issued = reinterpret_cast<volatile int*>(tail + 16);     // [2] k blocks issued per accumulator
 
   if (tid == 0) {
     *s_failed = 0;
-    for (int s = 0; s < MAX_STAGES; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_mdone + 8 * s, MMA_WARPS / 2); }
+    s_issued[0] = 0;
+    s_issued[1] = 0;
+    for (int s = 0; s < MAX_STAGES; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_mdone + 8 * s, 2); }
     for (int s = 0; s < NA; ++s) mbar_init(bar_afull + 8 * s, DQ_WARPS / 2);
     mbar_init(bar_done, MMA_WARPS);
-    mbar_init(bar_zero, DQ_WARPS);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -270,37 +266,47 @@ gemm_tiled_tc_kernel(const Params p, const __grid_constant__ CUtensorMap amap) {
     }
     __syncwarp();
   } else if (warp < DQ_WARP0 || warp >= DQ_WARP0 + DQ_WARPS) {
-    // ================= the eight MMA warps: lane 0 issues, the warp stays converged =================
+    // ================= the four MMA warps: lane 0 issues, the warp stays converged =================
     // Per k block an issuing warp spends ~800 cycles on fixed latencies (mbarrier test, fences, commit) and
-    // ~60-120 per tcgen05.mma, whatever the tile size, so one thread cannot feed eight small MMAs per k block:
-    // warp (set, hh, kp) issues the k steps 2 kp and 2 kp + 1 of accumulator hh for the k blocks of its set
-    // (even or odd).  Every MMA accumulates (the dequantisers zero the accumulators first), so the order in
-    // which the warps' MMAs reach the tensor core does not matter.  The dequantisers' arrival on afull also
-    // covers the stage's copies, which they waited for.
+    // 60-120 per tcgen05.mma, whatever the tile size, so one thread cannot feed eight small MMAs per k block.
+    // Warp (hh, set) issues the four k steps of accumulator hh for the k blocks of its set (even or odd).
+    // The MMAs of an accumulator reach the tensor core in k order all the same — fp32 accumulation is not
+    // associative, and the result must not depend on which warp was faster: a warp issues block i only after
+    // the other warp of its accumulator has published block i - 1 in shared memory (tcgen05 fences around
+    // the hand-over), so the two warps overlap their waits and commits but not their MMAs.
+    // The dequantisers' arrival on afull also covers the stage's copies, which they waited for.
     // instruction descriptor: D fp32, A and B fp16 and K-major, N = Mpad, M = 128
-    const int mi = (warp < DQ_WARP0) ? warp - 1 : warp - (DQ_WARP0 + DQ_WARPS) + 3;
-    const int hh = (mi >> 1) & 1, kp = mi & 1, mset = mi >> 2;
+    const int mi = (warp < DQ_WARP0) ? warp - 1 : 3;
+    const int hh = mi & 1, mset = mi >> 1;
     const uint32_t idesc = (1u << 4) | ((uint32_t)(p.Mpad >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (!mbar_wait(bar_zero, 0)) failed = true;
     TTC_ROLE_DECL
     for (int i = mset; i < nblk && !failed; i += 2) {
       const int s = i % S, ab = i % NA;
       TTC_ROLE(1, i, 0);
       if (!mbar_wait(bar_afull + 8 * ab, (uint32_t)((i / NA) & 1))) { failed = true; break; }
       TTC_ROLE(1, i, 1);
+      int ok = 1;
+      if (lane == 0) {
+        unsigned spins = 0;
+        while (s_issued[hh] != i && ++spins < (SPIN_LIMIT << 4)) { }
+        ok = s_issued[hh] == i;
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) { failed = true; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (lane == 0) {
         const uint64_t bd0 = kmajor_desc(ring + s * stage_bytes + RAW_PAD);
         const uint32_t a0 = tmem + A_COL0 + ab * 64 + hh * 32;
 #pragma unroll
-        for (int k2 = 0; k2 < 2; ++k2) {
-          const int ks = 2 * kp + k2;
-          mma_ts(tmem + hh * ACC_COLS, a0 + ks * 8, bd0 + (uint64_t)((ks * 32) >> 4), idesc, 1u);
-        }
+        for (int ks = 0; ks < BK / 16; ++ks)
+          mma_ts(tmem + hh * ACC_COLS, a0 + ks * 8, bd0 + (uint64_t)((ks * 32) >> 4), idesc,
+                 (i > 0 || ks > 0) ? 1u : 0u);
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        s_issued[hh] = i + 1;
         TTC_ROLE(1, i, 3);
         commit(bar_mdone + 8 * s);                  // the stage and the A buffer may be refilled when the MMAs
-      }                                             // of the set's four warps are done
+      }                                             // of both accumulators are done
       TTC_ROLE(1, i, 6);
       __syncwarp();
     }
@@ -317,13 +323,6 @@ gemm_tiled_tc_kernel(const Params p, const __grid_constant__ CUtensorMap amap) {
     const int t = lane & 3;
     const unsigned char* lane_w = gbase + (q * 32 + lane) * 16 + (quad & 1) * 8;     // words of tiles 2 (quad & 1), + 1
     const unsigned char* lane_s = gbase + 2048 + q * 32 + t * 8;
-    // zero this warp's lanes of accumulator hh (the sets take the 16-column chunks in turn)
-    for (int ch = dset; ch < p.Mpad / 16; ch += 2)
-      st_zero16(tmem + ((uint32_t)(32 * quad) << 16) + hh * ACC_COLS + ch * 16);
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar_zero);
     TTC_ROLE_DECL
     for (int i = dset; i < nblk; i += 2) {                    // the set's k blocks
       const int s = i % S, ab = i % NA;

@@ -161,11 +161,13 @@ def matmul_q40(a: torch.Tensor, b_w: torch.Tensor, b_s: torch.Tensor, b_shape, *
     a [M,K] fp16 contiguous, b_w/b_s the packed weight and scales of a [K,N] matrix
     quantised row-major (groups along N), b_shape = (K, N).  Returns fp16 [M,N].
 
-    Up to 16 rows with N % 256 == 0 the weight is read through a tiled copy that is made the first time
-    a given (b_w, b_s) pair of tensors is seen and kept while those tensor objects live and are not
-    written in place (the reference's LinearQ4_0 passes the same `.w` / `.s` attributes on every call,
-    hf_model_q40_kv_shared.py:228-236).  The copy doubles the device memory of that weight;
-    `relayout=False` (or relayout_cache_config(enabled=False)) reads the checkpoint layout instead."""
+    With N % 256 == 0 the weight is read through a tiled copy that is made the first time a given
+    (b_w, b_s) pair of tensors is seen and kept while those tensor objects live and are not written in
+    place (the reference's LinearQ4_0 passes the same `.w` / `.s` attributes on every call,
+    hf_model_q40_kv_shared.py:228-236): up to 16 rows by the decode step's tiled kernel, above (with
+    K % 64 == 0) by the tensor-core kernel that writes the dequantised operand to tensor memory.  The copy
+    doubles the device memory of that weight; `relayout=False` (or relayout_cache_config(enabled=False))
+    reads the checkpoint layout instead."""
     dev = _need_cuda(a, b_w, b_s)
     assert a.is_contiguous(), "Matrix A must be contiguous"
     M, K = a.shape
@@ -192,6 +194,23 @@ def matmul_q40(a: torch.Tensor, b_w: torch.Tensor, b_s: torch.Tensor, b_shape, *
             return c
     if small and N % 128 == 0 and _cluster_gemv(dev, a, b_w, b_s, c, M, N, K):
         return c
+    wide = (M > 16 and group_size == 64 and N % 256 == 0 and K % 64 == 0 and a.data_ptr() % 16 == 0 and
+            c.stride(1) == 1 and c.stride(0) % 2 == 0 and c.data_ptr() % 4 == 0)
+    if wide and (relayout if relayout is not None else _relayout_cfg["enabled"]):
+        n_before = len(_relayout_cache)
+        tiled = _tiled_copy_of(b_w, b_s, K, N)
+        if tiled is not None:
+            import ctypes
+            ws = _workspace("gemm", dev, 4096, zero=True)        # its last word is the error word of tc_error_flag()
+            P1 = ctypes.c_void_p * 1
+            rc = lib.q40_gemm_tiled_tc_multi(1, a.data_ptr(), a.stride(0), P1(tiled.data_ptr()), P1(c.data_ptr()),
+                                             (ctypes.c_int64 * 1)(c.stride(0)), (ctypes.c_int * 1)(N), M, K,
+                                             ws.data_ptr() + 4092, 1 if len(_relayout_cache) == n_before else 0,
+                                             _stream(dev))
+            if rc == 0:
+                return c
+            if rc != -5:        # Q40_E_UNSUPPORTED: no tensor-map encoder in this driver -> checkpoint layout
+                check(rc, "q40_gemm_tiled_tc_multi")
     nbytes = lib.q40_gemm_workspace_bytes(M, N, K)
     ws = _workspace("gemm", dev, nbytes, zero=True)
     check(lib.q40_gemm_kn(a.data_ptr(), a.stride(0), b_w.data_ptr(), b_s.data_ptr(), c.data_ptr(),

@@ -314,7 +314,8 @@ class Transformer(nn.Module):
             if self._tc_err is None:
                 self._tc_err = torch.zeros(1, dtype=torch.int32, device=self.device)
             return K.gemm_tiled_tc(x, [(t, l.kn()) for t, l in zip(self._tiled_of(lins), lins)], err=self._tc_err)
-        return [K.matmul_q40(x, l.w, l.s, l.kn(), group_size=l.group_size) for l in lins]
+        # relayout=False: the checkpoint-layout kernels, whose summation order the 7B token parity was taken with
+        return [K.matmul_q40(x, l.w, l.s, l.kn(), group_size=l.group_size, relayout=False) for l in lins]
 
     # ------------------------------------------------------------------ decode
     def _step_buffers(self, B):
