@@ -62,6 +62,7 @@ struct Params {
   int64_t ldc[3];
   int N[3], spans[3], nprob;
   int M, K, Mpad, rows_per_split, stages;
+  int split_acc;          // Mpad <= 64: even and odd k blocks have accumulators of their own
   int* err;               // device word, set non-zero when a bounded wait expired
   void* trace;            // stage timestamps (trace builds only)
 };
@@ -269,11 +270,13 @@ gemm_tiled_tc_kernel(const Params p, const __grid_constant__ CUtensorMap amap) {
     // ================= the four MMA warps: lane 0 issues, the warp stays converged =================
     // Per k block an issuing warp spends ~800 cycles on fixed latencies (mbarrier test, fences, commit) and
     // 60-120 per tcgen05.mma, whatever the tile size, so one thread cannot feed eight small MMAs per k block.
-    // Warp (hh, set) issues the four k steps of accumulator hh for the k blocks of its set (even or odd).
-    // The MMAs of an accumulator reach the tensor core in k order all the same — fp32 accumulation is not
-    // associative, and the result must not depend on which warp was faster: a warp issues block i only after
-    // the other warp of its accumulator has published block i - 1 in shared memory (tcgen05 fences around
-    // the hand-over), so the two warps overlap their waits and commits but not their MMAs.
+    // Warp (hh, set) issues the four k steps of feature half hh for the k blocks of its set (even or odd).
+    // fp32 accumulation is not associative, and the result must not depend on which warp was faster, so every
+    // accumulator has to see its MMAs in a fixed order.  Up to 64 padded batch rows tensor memory has room for
+    // an accumulator per (half, set): each warp owns one and the epilogue adds even + odd.  Above, the two
+    // warps of a half share one accumulator: a warp issues block i only after the other has published block
+    // i - 1 in shared memory (tcgen05 fences around the hand-over), so their waits and commits overlap but not
+    // their MMAs (about 10 % slower than issuing in arbitrary order).
     // The dequantisers' arrival on afull also covers the stage's copies, which they waited for.
     // instruction descriptor: D fp32, A and B fp16 and K-major, N = Mpad, M = 128
     const int mi = (warp < DQ_WARP0) ? warp - 1 : 3;
@@ -287,7 +290,7 @@ gemm_tiled_tc_kernel(const Params p, const __grid_constant__ CUtensorMap amap) {
       if (!mbar_wait(bar_afull + 8 * ab, (uint32_t)((i / NA) & 1))) { failed = true; break; }
       TTC_ROLE(1, i, 1);
       int ok = 1;
-      if (lane == 0) {
+      if (lane == 0 && !p.split_acc) {
         unsigned spins = 0;
         while (s_issued[hh] != i && ++spins < (SPIN_LIMIT << 4)) { }
         ok = s_issued[hh] == i;
@@ -300,8 +303,8 @@ gemm_tiled_tc_kernel(const Params p, const __grid_constant__ CUtensorMap amap) {
         const uint32_t a0 = tmem + A_COL0 + ab * 64 + hh * 32;
 #pragma unroll
         for (int ks = 0; ks < BK / 16; ++ks)
-          mma_ts(tmem + hh * ACC_COLS, a0 + ks * 8, bd0 + (uint64_t)((ks * 32) >> 4), idesc,
-                 (i > 0 || ks > 0) ? 1u : 0u);
+          mma_ts(tmem + (p.split_acc ? (2 * hh + mset) * 64 : hh * ACC_COLS), a0 + ks * 8,
+                 bd0 + (uint64_t)((ks * 32) >> 4), idesc, (i > (p.split_acc ? mset : 0) || ks > 0) ? 1u : 0u);
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         s_issued[hh] = i + 1;
         TTC_ROLE(1, i, 3);
@@ -386,8 +389,21 @@ gemm_tiled_tc_kernel(const Params p, const __grid_constant__ CUtensorMap amap) {
     const int nchunk = p.Mpad / 16;
     for (int ch = dset; ch < nchunk; ch += 2) {
       uint32_t r[16];
-      ld16(tmem + ((uint32_t)(32 * quad) << 16) + hh * ACC_COLS + ch * 16, r);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      const uint32_t lane_base = tmem + ((uint32_t)(32 * quad) << 16);
+      if (p.split_acc) {
+        // even blocks + odd blocks (the odd accumulator was never written when the k range is one block)
+        uint32_t r2[16];
+        ld16(lane_base + (2 * hh) * 64 + ch * 16, r);
+        ld16(lane_base + (2 * hh + 1) * 64 + ch * 16, r2);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (nblk > 1) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+        }
+      } else {
+        ld16(lane_base + hh * ACC_COLS + ch * 16, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      }
 #pragma unroll
       for (int j = 0; j < 16; ++j) tile_f[(ch * 16 + j) * SPAN + feat] = __uint_as_float(r[j]);
     }
@@ -518,6 +534,7 @@ extern "C" int q40_gemm_tiled_tc_multi(int nmat, const void* a, int64_t lda, con
       p.N[i] = n_cols[i]; p.spans[i] = n_cols[i] / SPAN;
     }
     p.M = mc; p.K = K; p.Mpad = (mc + 15) / 16 * 16;
+    p.split_acc = p.Mpad <= 64 ? 1 : 0;
     p.err = err;
 #ifdef Q40_TRACE
     p.trace = q40_trace_ptr;

@@ -546,3 +546,22 @@ def test_causal_attention_matches_fp32_reference(K, S, H, Hkv):
     s = s.masked_fill(torch.ones((S, S), device="cuda", dtype=torch.bool).triu(1), float("-inf"))
     ref = (torch.softmax(s, dim=-1) @ vf).permute(1, 0, 2)
     assert_close(host(o), ref.cpu().numpy().astype(np.float16))
+
+
+@pytest.mark.parametrize("M,Kd", [(20, 64), (20, 128), (64, 192), (100, 64), (33, 4096)])
+def test_matmul_tiled_tc_short_and_long_k_ranges(K, M, Kd):
+    """One and two k blocks (the even / odd accumulators of the <= 64-row mode with nothing or one block each),
+    an odd block count, and a long k range; repeated calls are bit-identical."""
+    rng = np.random.default_rng(M * 7 + Kd)
+    N = 512
+    a = (rng.standard_normal((M, Kd)) * 0.5).astype(np.float16)
+    w = (rng.standard_normal((Kd, N)) * 0.3).astype(np.float16)
+    q, s = O.quantize_q40(w, 64)
+    t = K.relayout_tiled(dev(q), dev(s), (Kd, N))
+    a_d = dev(a)
+    c1 = K.gemm_tiled_tc(a_d, [(t, (Kd, N))])[0]
+    c2 = K.gemm_tiled_tc(a_d, [(t, (Kd, N))])[0]
+    assert torch.equal(c1, c2)
+    ref = O.matmul_q40(a, q, s, (Kd, N))
+    scale = max(1.0, float(np.abs(ref.astype(np.float32)).mean()))
+    assert_close(host(c1), ref, atol=ATOL * scale)
