@@ -224,6 +224,9 @@ class Transformer(nn.Module):
         # the prompt pass keeps the checkpoint-layout tensor-core matmul by default: the tiled-copy kernel sums
         # k in a different order, which flips greedy tokens at near-ties against the 7B reference run
         self.prefill_tiled_tc = False
+        # True: the prompt pass returns logits of the last position only, [1, 1, vocab] (all a caller that
+        # samples the next token needs); False: of every position like the reference
+        self.prefill_last_only = False
         self._tc_err = None         # device word the prompt pass's tensor-core launches set on a wait expiry
         # ... True: through the byte-balanced stream-K launch (one CTA per SM, bulk-copy ring, no clusters);
         # False: the cluster-reduced launch on the same tiled copies (faster on B200, the default)
@@ -302,8 +305,11 @@ class Transformer(nn.Module):
         self._prefix_len_dev.fill_(S)
         if self._tc_err is not None and int(self._tc_err.item()) != 0:
             raise K.Q40Error("prompt pass: a bounded wait inside a tensor-core matmul expired")
+        if self.prefill_last_only:
+            # the tree search reads the last position only (mcts.py:105); the reference computes all S rows
+            h = h[S - 1:]
         hn = K.rmsnorm(h, self.norm.weight, p.norm_eps)
-        return F.linear(hn, self.output.weight).to(DTYPE).view(1, S, -1)
+        return F.linear(hn, self.output.weight).to(DTYPE).view(1, h.shape[0], -1)
 
     def _mm(self, x, lins):
         """[x @ deq(W_i)] for projections that share the activations x [M, K] (prompt pass): one tensor-core

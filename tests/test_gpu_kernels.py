@@ -322,7 +322,7 @@ def test_attn_shared_prefix_vs_oracle(K, B, H, Hkv, prefix):
 
 def test_attn_shared_prefix_config3_geometry(K):
     """32 heads, head_dim 128, prefix 2048, 64 branches with suffix lengths U[0,256] in 16-token
-    pages: compared with the unshared paged kernel and, for three branches, the oracle."""
+    pages: every branch against the oracle (a few seconds of numpy)."""
     rng = np.random.default_rng(0)
     B, H, prefix = 64, 32, 2048
     lens = list(rng.integers(0, 257, size=B))
@@ -331,9 +331,8 @@ def test_attn_shared_prefix_config3_geometry(K):
     pv = rng.standard_normal((prefix, H, 128)).astype(np.float16)
     sl = np.array(lens, dtype=np.int32)
     o = K.shared_prefix_attn(dev(q), dev(pk), dev(pv), prefix, dev(tbl), dev(sl), dev(kp), dev(vp), page_size=16)
-    sub = [0, 31, 63]
-    ref = O.attn_shared_prefix(q[sub], pk, pv, prefix, tbl[sub], sl[sub], kp, vp, 16)
-    assert_close(host(o)[sub], ref)
+    ref = O.attn_shared_prefix(q, pk, pv, prefix, tbl, sl, kp, vp, 16)
+    assert_close(host(o), ref)
 
 
 def test_triton_attn_wrapper(K):

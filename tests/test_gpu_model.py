@@ -254,6 +254,13 @@ def test_prefill_tiled_tc_matches_default_prefill(small):
             lg = m(torch.from_numpy(g["prompt"]).cuda(), 0)
         outs.append((lg[0].float().cpu().numpy(), m.layers[-1].attention.cache_prompt_k.float().cpu().numpy().copy()))
     (l0, k0), (l1, k1) = outs
+    # prefill_last_only: the same last row, nothing else
+    m = build_model(g, False)
+    m.prefill_last_only = True
+    with torch.inference_mode():
+        last = m(torch.from_numpy(g["prompt"]).cuda(), 0)
+    assert last.shape == (1, 1, l0.shape[-1])
+    np.testing.assert_array_equal(last[0, 0].float().cpu().numpy(), l0[-1])
     logits_close(l1[-1], g["prefill_logits_last"])
     np.testing.assert_allclose(l1, l0, rtol=2e-2, atol=0.15)
     np.testing.assert_allclose(k1, k0, rtol=2e-2, atol=2e-2)
