@@ -297,6 +297,63 @@ def timed_e2e(model, width, steps, warmup, prompt_len):
     return e0.elapsed_time(e1) * 1e-3, width * 8, width * 8
 
 
+def tree_step_timing(dev, branches=100, reps=50):
+    """The device-side sampling step of the tree search (mcts.py:94-178: temperature, top-k(32), softmax, counted
+    draws, unique tokens, fork bookkeeping, terminal detection) for `branches` live branches on fp16 logits
+    [branches, 32016]: two launches, timed with CUDA events from a graph; no fork happens (all particles live),
+    so the cache copy launch is not part of it."""
+    import torch
+    from spec_mcts_b200._lib import check, lib
+    from spec_mcts_b200.tree import TERMINAL_SEQ
+    g = torch.Generator(device=dev).manual_seed(7)
+    B, V, max_new = branches, VOCAB, 64
+    logits = (torch.randn((B, V), generator=g, device=dev) * 2.0).to(torch.float16)
+    u = torch.rand((B, B), generator=g, device=dev)
+    i32 = dict(dtype=torch.int32, device=dev)
+    results = torch.zeros((B, max_new), dtype=torch.int64, device=dev)
+    results_len, counts = torch.zeros(B, **i32), torch.ones(B, **i32)
+    alive = torch.ones(B, dtype=torch.uint8, device=dev)
+    last_tok, end_state, n_unique, fork_src = (torch.zeros(B, **i32) for _ in range(4))
+    uni_tok, uni_cnt = torch.zeros((B, 32), **i32), torch.zeros((B, 32), **i32)
+    batch_stats = torch.zeros(max_new, dtype=torch.uint8, device=dev)
+    term = torch.tensor(TERMINAL_SEQ, dtype=torch.int64, device=dev)
+    ctl = torch.tensor([B, 0, 0, 0], **i32)
+
+    def step():
+        st = torch.cuda.current_stream(dev).cuda_stream
+        check(lib.q40_tree_sample(logits.data_ptr(), logits.stride(0), B, V, 32, 0.3, 0.0, counts.data_ptr(),
+                                  u.data_ptr(), u.stride(0), n_unique.data_ptr(), uni_tok.data_ptr(),
+                                  uni_cnt.data_ptr(), None, None, st), "q40_tree_sample")
+        check(lib.q40_tree_fork(n_unique.data_ptr(), uni_tok.data_ptr(), uni_cnt.data_ptr(), results.data_ptr(),
+                                max_new, 0, B, counts.data_ptr(), last_tok.data_ptr(), alive.data_ptr(),
+                                results_len.data_ptr(), end_state.data_ptr(), term.data_ptr(), len(TERMINAL_SEQ), 2,
+                                ctl.data_ptr(), fork_src.data_ptr(), ctl.data_ptr() + 4, ctl.data_ptr() + 8,
+                                batch_stats.data_ptr(), ctl.data_ptr() + 12, st), "q40_tree_fork")
+
+    step()
+    torch.cuda.synchronize(dev)
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    torch.cuda.synchronize(dev)
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        step()
+    for _ in range(3):
+        gr.replay()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        gr.replay()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    return {"what": "tree-search sampling step on the device (sample + fork bookkeeping), %d live branches" % B,
+            "us_per_step": e0.elapsed_time(e1) * 1e3 / reps, "launches": 2}
+
+
 def reference_class_on_drop_in(model, dev, steps=16):
     """tokens/s at width 1 of the reference's own Transformer class (when its files are staged under
     baseline/_ref), imported against this repository's triton_kernels module and given this model's
@@ -904,6 +961,7 @@ def main():
             by_path = {"tiled (default)": {"ms_per_step": results[widths[0]] / steps * 1e3},
                        "checkpoint layout, reference operand rounding": {"ms_per_step": sec_ref / min(steps, 32) * 1e3}}
         drop_in = reference_class_on_drop_in(model, dev) if rank == 0 and world == 1 and not args.no_extras else None
+        tree_step = tree_step_timing(dev, max(widths)) if rank == 0 and world == 1 and not args.no_extras else None
         model.release_graphs()
 
     kernels = None
@@ -952,6 +1010,8 @@ def main():
             line["by_path"] = by_path
         if drop_in is not None:
             line["drop_in"] = drop_in
+        if tree_step is not None:
+            line["tree_step"] = tree_step
         if kernels is not None:
             line["kernels"] = kernels
         if tp is not None:

@@ -17,7 +17,7 @@ namespace q40 {
 namespace tree {
 
 constexpr int TOPK_MAX = 32;
-constexpr int THREADS = 256;
+constexpr int THREADS = 1024;     // one CTA per branch: 32 warps hide the latency of the division per element
 
 // monotone map float -> uint32
 __device__ __forceinline__ uint32_t fkey(float v) {
@@ -40,7 +40,10 @@ struct SampleParams {
   int32_t* uni_cnt;        // [B, 32]
   float* probs_out;        // [B, 32] candidate probabilities in candidate order (optional)
   int32_t* cand_out;       // [B, 32] candidate token ids in candidate order (optional)
+  int use_cache;           // 4 V bytes of dynamic shared memory hold the row's order keys
 };
+
+constexpr int EQ_LIST = 128;     // ties with the k-th largest value that are ranked from a list; more fall back to a scan
 
 __global__ void __launch_bounds__(THREADS) sample_kernel(const SampleParams p) {
   __shared__ unsigned int hist[256];
@@ -61,49 +64,104 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const SampleParams p) {
     const float x = __fdiv_rn(__half2float(row[i]), tdiv);
     return fixed ? __half2float(__float2half_rn(x)) : x;
   };
+  // the order keys of the whole row, computed once (a division per element) and kept in shared memory when
+  // the row fits (use_cache: 4 V bytes were granted at launch); the passes below read them from there
+  extern __shared__ uint32_t key_cache[];
+  const bool cached = p.use_cache != 0;
+  if (cached) {
+    for (int i = tid; i < p.V; i += THREADS) key_cache[i] = fkey(scaled(i));
+    __syncthreads();
+  }
+  auto key_of = [&](int i) { return cached ? key_cache[i] : fkey(scaled(i)); };
 
   // ---- the k-th largest key by radix selection, most significant byte first ----
   if (tid == 0) { s_prefix = 0; s_need = (uint32_t)k; }
   __syncthreads();
   for (int pass = 0; pass < 4; ++pass) {
     const int shift = 24 - 8 * pass;
-    hist[tid] = 0;
+    if (tid < 256) hist[tid] = 0;
     __syncthreads();
     const uint32_t prefix = s_prefix, mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
-    for (int i = tid; i < p.V; i += THREADS) {
-      const uint32_t key = fkey(scaled(i));
-      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFF], 1u);
+    // fp16 logits of one row share a handful of leading bytes, so the lanes of a warp mostly hit the same bin:
+    // one shared-memory atomic per distinct bin and warp (match_any) instead of one per element
+    for (int base = 0; base < p.V; base += THREADS) {
+      const int i = base + tid;
+      uint32_t bin = 0xFFFFFFFFu;
+      if (i < p.V) {
+        const uint32_t key = key_of(i);
+        if ((key & mask) == prefix) bin = (key >> shift) & 0xFF;
+      }
+      if (pass == 0) {
+        const unsigned peers = __match_any_sync(0xffffffffu, bin);
+        if (bin != 0xFFFFFFFFu && (tid & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], (unsigned)__popc(peers));
+      } else if (bin != 0xFFFFFFFFu) {
+        atomicAdd(&hist[bin], 1u);          // later passes: few keys left, spread over the bins
+      }
     }
     __syncthreads();
-    if (tid == 0) {
-      uint32_t need = s_need;
-      int bin = 255;
-      for (; bin > 0; --bin) {
-        if (hist[bin] >= need) break;
-        need -= hist[bin];
+    if (tid < 32) {
+      // the highest bin b with count(bins > b) < need <= count(bins >= b): lane l owns bins 8l .. 8l + 7;
+      // suffix sums across the lanes by shuffles instead of one thread walking 256 counters
+      const uint32_t need0 = s_need;
+      uint32_t mine[8], tot = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { mine[j] = hist[8 * tid + j]; tot += mine[j]; }
+      uint32_t above = 0;                 // keys in the bins of higher lanes
+      for (int l = 31; l > 0; --l) {
+        const uint32_t v = __shfl_sync(0xffffffffu, tot, l);
+        if (tid < l) above += v;
       }
-      s_prefix = prefix | ((uint32_t)bin << shift);
-      s_need = need;                     // how many keys equal to the final threshold are taken
+      // the lane whose bins contain the threshold: above < need0 <= above + tot (lane 0 takes the rest)
+      const bool has = (above < need0 && need0 <= above + tot) || (tid == 0 && need0 > above + tot);
+      if (has) {
+        uint32_t need = need0 - above;
+        int j = 7;
+        for (; j > 0; --j) {
+          if (mine[j] >= need) break;
+          need -= mine[j];
+        }
+        s_prefix = prefix | ((uint32_t)(8 * tid + j) << shift);
+        s_need = need;                    // how many keys equal to the final threshold are taken
+      }
     }
     __syncthreads();
   }
   const uint32_t thr = s_prefix;
   const int eq_take = (int)s_need;
   // ---- collect: every key above the threshold, and the eq_take smallest token ids among the equal ones ----
-  if (tid == 0) { c_n = 0; c_eq_taken = 0; }
+  __shared__ int e_n, e_idx[EQ_LIST];
+  if (tid == 0) { c_n = 0; c_eq_taken = 0; e_n = 0; }
   __syncthreads();
   for (int i = tid; i < p.V; i += THREADS) {
-    const uint32_t key = fkey(scaled(i));
+    const uint32_t key = key_of(i);
     if (key > thr) {
       const int s = atomicAdd(&c_n, 1);
       c_key[s] = key; c_idx[s] = i;
+    } else if (key == thr) {
+      const int s = atomicAdd(&e_n, 1);          // ties with the threshold are rare: list them
+      if (s < EQ_LIST) e_idx[s] = i;
     }
   }
   __syncthreads();
+  if (e_n <= EQ_LIST) {
+    // the eq_take smallest token ids of the list (rank by counting smaller ids), no scan over the row
+    if (tid < e_n) {
+      const int mi = e_idx[tid];
+      int rank = 0;
+      for (int j = 0; j < e_n; ++j) rank += e_idx[j] < mi ? 1 : 0;
+      if (rank < eq_take) {
+        const int s = atomicAdd(&c_n, 1);
+        c_key[s] = thr; c_idx[s] = mi;
+      }
+    }
+    __syncthreads();
+    if (tid == 0) c_eq_taken = eq_take;
+    __syncthreads();
+  }
   // equal keys in ascending token order: blocks of THREADS consecutive ids, ranked by ballot inside a block
   for (int base = 0; base < p.V && c_eq_taken < eq_take; base += THREADS) {
     const int i = base + tid;
-    const bool eq = i < p.V && fkey(scaled(i)) == thr;
+    const bool eq = i < p.V && key_of(i) == thr;
     __shared__ int warp_cnt[THREADS / 32];
     const unsigned bal = __ballot_sync(0xffffffffu, eq);
     if ((tid & 31) == 0) warp_cnt[tid >> 5] = __popc(bal);
@@ -198,35 +256,52 @@ struct ForkParams {
   int32_t* all_done;         // [1]
 };
 
+constexpr int FORK_MAX_BRANCHES = 1024;     // branches whose bookkeeping is staged in shared memory
+
 __global__ void __launch_bounds__(THREADS) fork_kernel(const ForkParams p) {
-  __shared__ int s_curr0, s_curr1;
+  __shared__ int s_curr0, s_curr1, s_dead;
+  __shared__ short s_nu[FORK_MAX_BRANCHES], s_start[FORK_MAX_BRANCHES], s_forks[FORK_MAX_BRANCHES];
   const int tid = threadIdx.x;
-  // ---- sequential part (mcts.py:127-154): the order of the branches decides who gets the room ----
+  // ---- who forks how often (mcts.py:127-154): the order of the branches decides who gets the room.  The
+  // inputs are staged in shared memory by all threads, the sequential walk touches shared memory only, and
+  // the results are written back by all threads (a single thread walking global memory costs ~1.5 us per
+  // branch) ----
+  const int curr_in = *p.curr;
+  for (int i = tid; i < curr_in; i += THREADS) s_nu[i] = p.alive[i] ? (short)p.n_unique[i] : (short)0;
+  __syncthreads();
   if (tid == 0) {
-    int curr = *p.curr;
-    const int curr0 = curr;
-    for (int i = 0; i < curr0; ++i) {
-      if (!p.alive[i]) continue;
-      const int nu = p.n_unique[i];
-      p.last_tok[i] = p.uni_tok[i * TOPK_MAX];
-      p.counts[i] = p.uni_cnt[i * TOPK_MAX];
-      p.results[(int64_t)i * p.max_new + p.step] = p.uni_tok[i * TOPK_MAX];
-      int forks = min(nu - 1, p.batch - curr);
-      if (forks > 0 && curr < p.batch) {
-        for (int j = 0; j < forks; ++j) {
-          p.fork_src[curr + j] = i;
-          p.last_tok[curr + j] = p.uni_tok[i * TOPK_MAX + 1 + j];
-          p.counts[curr + j] = p.uni_cnt[i * TOPK_MAX + 1 + j];
-        }
-        curr += forks;
+    int curr = curr_in;
+    for (int i = 0; i < curr_in; ++i) {
+      int forks = 0;
+      if (s_nu[i] > 0) {
+        forks = min((int)s_nu[i] - 1, p.batch - curr);
+        if (forks < 0 || curr >= p.batch) forks = 0;
       }
+      s_start[i] = (short)curr;
+      s_forks[i] = (short)forks;
+      curr += forks;
     }
-    s_curr0 = curr0; s_curr1 = curr;
+    s_curr0 = curr_in; s_curr1 = curr; s_dead = 0;
     *p.curr = curr;
-    *p.n_forks = curr - curr0;
-    *p.fork_base = curr0;
+    *p.n_forks = curr - curr_in;
+    *p.fork_base = curr_in;
     p.batch_stats[p.step] = (uint8_t)curr;
   }
+  __syncthreads();
+  for (int i = tid; i < curr_in; i += THREADS) {
+    if (s_nu[i] == 0) continue;                 // not alive
+    const int32_t tok0 = p.uni_tok[i * TOPK_MAX];
+    p.last_tok[i] = tok0;
+    p.counts[i] = p.uni_cnt[i * TOPK_MAX];
+    p.results[(int64_t)i * p.max_new + p.step] = tok0;
+    const int start = s_start[i], forks = s_forks[i];
+    for (int j = 0; j < forks; ++j) {
+      p.fork_src[start + j] = i;
+      p.last_tok[start + j] = p.uni_tok[i * TOPK_MAX + 1 + j];
+      p.counts[start + j] = p.uni_cnt[i * TOPK_MAX + 1 + j];
+    }
+  }
+  __threadfence_block();
   __syncthreads();
   const int curr0 = s_curr0, curr1 = s_curr1;
   // ---- the new branches inherit the token history of their origin, then take their own token ----
@@ -252,14 +327,11 @@ __global__ void __launch_bounds__(THREADS) fork_kernel(const ForkParams p) {
     p.end_state[i] = st;
     p.results_len[i] += alive ? 1 : 0;
     p.alive[i] = (alive && !end) ? 1 : 0;
+    if (!(alive && !end)) atomicAdd(&s_dead, 1);
   }
   __syncthreads();
-  if (tid == 0) {
-    int dead = 0;
-    for (int i = 0; i < p.batch; ++i) dead += p.alive[i] ? 0 : 1;
-    // the reference stops when the number of finished rows equals the live branch count (mcts.py:174)
-    *p.all_done = (dead == curr1) ? 1 : 0;
-  }
+  // the reference stops when the number of finished rows equals the live branch count (mcts.py:174)
+  if (tid == 0) *p.all_done = (s_dead == curr1) ? 1 : 0;
 }
 
 // Copy the Q4_0 suffix rows [0, len) of branch fork_src[nb] to branch nb for every layer, for the branches
@@ -293,7 +365,18 @@ extern "C" int q40_tree_sample(const void* logits, int64_t ld, int B, int V, int
   p.logits = (const __half*)logits; p.ld = ld; p.V = V; p.top_k = top_k; p.temp = temp; p.slope = slope;
   p.counts = counts; p.draws = draws; p.draws_ld = draws_ld; p.n_unique = n_unique; p.uni_tok = uni_tok;
   p.uni_cnt = uni_cnt; p.probs_out = probs_out; p.cand_out = cand_out;
-  sample_kernel<<<B, THREADS, 0, (cudaStream_t)stream>>>(p);
+  // the row's order keys in dynamic shared memory when they fit beside the static arrays
+  size_t smem = 0;
+  if ((size_t)V * 4 <= 200 * 1024) {
+    smem = (size_t)V * 4;
+    if (smem > 40 * 1024 &&
+        cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      (void)cudaGetLastError();
+      smem = 0;
+    }
+  }
+  p.use_cache = smem ? 1 : 0;
+  sample_kernel<<<B, THREADS, smem, (cudaStream_t)stream>>>(p);
   Q40_LAUNCH_CHECK();
   return Q40_OK;
 }
@@ -309,6 +392,7 @@ extern "C" int q40_tree_fork(const int32_t* n_unique, const int32_t* uni_tok, co
       !curr || !fork_src || !n_forks || !fork_base || !batch_stats || !all_done || (term_len > 0 && !term_seq))
     return Q40_E_NULL;
   if (batch < 1 || max_new < 1 || step < 0 || step >= max_new || term_len < 0) return Q40_E_SHAPE;
+  if (batch > FORK_MAX_BRANCHES) return Q40_E_UNSUPPORTED;
   ForkParams p{};
   p.n_unique = n_unique; p.uni_tok = uni_tok; p.uni_cnt = uni_cnt; p.results = results; p.max_new = max_new;
   p.step = step; p.batch = batch; p.counts = counts; p.last_tok = last_tok; p.alive = alive;

@@ -56,8 +56,9 @@ def test_tree_search_matches_reference_loop(name):
     np.testing.assert_array_equal(np.array(model.fork_calls, dtype=np.int64).reshape(-1, 4), G[name + ".forks"])
 
 
+@pytest.mark.parametrize("V", [5000, 300])
 @pytest.mark.parametrize("temp", [0.3, -0.8, 1.0])
-def test_tree_sample_candidates_and_counts_vs_oracle(temp):
+def test_tree_sample_candidates_and_counts_vs_oracle(temp, V):
     """Plain random logits (ties among the top values do occur in fp16): candidate order, probabilities
     and the counted draws against oracle/tree_oracle.py."""
     if not torch.cuda.is_available():
@@ -65,9 +66,10 @@ def test_tree_sample_candidates_and_counts_vs_oracle(temp):
     from oracle import tree_oracle as T
     from spec_mcts_b200._lib import check, lib
     rng = np.random.default_rng(5)
-    B, V, batch = 7, 5000, 40
+    B, batch = 7, 40
     logits = (rng.standard_normal((B, V)) * 2).astype(np.float16)
-    logits[3, :100] = np.float16(7.5)              # a row whose top candidates all tie
+    logits[3, :100] = np.float16(7.5)              # a row whose top candidates all tie (ranked from the kernel's tie list)
+    logits[5, V // 5:V // 5 + min(400, V // 2)] = np.float16(9.0)     # ... and more ties than that list holds (the ordered scan)
     counts = np.array([1, 40, 3, 17, 2, 9, 5], dtype=np.int32)
     draws = rng.random((B, batch), dtype=np.float32)
     slope = np.float32((abs(temp) - 0.1) / (batch - 1))
