@@ -107,8 +107,10 @@ int q40_gemm_kn_tc_multi(int nmat, const void* a, int64_t lda, const void* const
  * so that a caller that already holds tiled copies for the narrow decode path needs no second format:
  * the weight stream of a CTA is one contiguous run fetched by 1-D bulk copies, the activations arrive by
  * tiled TMA copies (a tensor map over `a` is encoded per call), both into a 3..6 stage ring; A operand
- * value fp16(code * scale) as in the reference (triton_kernels.py:444-445).  Same `err`, `use_pdl` and
- * row-chunk rules as q40_gemm_kn_tc_multi; Q40_E_UNSUPPORTED when the driver offers no tensor-map encoder. */
+ * value fp16(code * scale) as in the reference (triton_kernels.py:444-445), written to tensor memory.  Batches
+ * above 128 rows run as consecutive launches of 128 rows.  Results are bit-identical from run to run.  Same
+ * `err` and `use_pdl` rules as q40_gemm_kn_tc_multi; Q40_E_UNSUPPORTED when the driver offers no tensor-map
+ * encoder. */
 int q40_gemm_tiled_tc_multi(int nmat, const void* a, int64_t lda, const void* const* bw_tiled, void* const* c,
                             const int64_t* ldc, const int* n_cols, int M, int K, int* err, int use_pdl,
                             void* stream);
