@@ -122,14 +122,23 @@ __global__ void __launch_bounds__(THREADS, 2) lm_head_kernel(const Params p) {
       const __half* wa = p.w + (int64_t)ra * p.K + kq * kq_len + 8 * t;
       const __half* wb = p.w + (int64_t)rb * p.K + kq * kq_len + 8 * t;
       const __half* xr = xs + kq * kq_len + 8 * t;
-      for (int k0 = 0; k0 < kq_len; k0 += 128) {
-        uint4 va[4], vb[4];
+      // the weights of the next 128 k are requested before the MMAs of the current ones (two batches of eight
+      // 16-byte loads in flight per lane)
+      uint4 na[4], nb[4];
+      auto fetch = [&](int k0, uint4 (&a4)[4], uint4 (&b4)[4]) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const bool ok = k0 + 32 * u < kq_len;
-          va[u] = ok ? ld_stream(wa + k0 + 32 * u) : make_uint4(0, 0, 0, 0);
-          vb[u] = ok ? ld_stream(wb + k0 + 32 * u) : make_uint4(0, 0, 0, 0);
+          a4[u] = ok ? ld_stream(wa + k0 + 32 * u) : make_uint4(0, 0, 0, 0);
+          b4[u] = ok ? ld_stream(wb + k0 + 32 * u) : make_uint4(0, 0, 0, 0);
         }
+      };
+      fetch(0, na, nb);
+      for (int k0 = 0; k0 < kq_len; k0 += 128) {
+        uint4 va[4], vb[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { va[u] = na[u]; vb[u] = nb[u]; }
+        if (k0 + 128 < kq_len) fetch(k0 + 128, na, nb);
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           if (k0 + 32 * u >= kq_len) break;
